@@ -25,15 +25,45 @@ from .pages import OutOfPages, PagePool, SlotPool
 
 @dataclass(frozen=True)
 class KVNeed:
-    """What one layer execution asks of the paged cache."""
+    """What one layer execution asks of the paged cache.
+
+    ``value_dim``: size of a value head where it differs from a key head's (None: the same).
+    ``pools``: block sizes P for which, beside the tokens, one mean key and value per P
+    tokens is kept for as long as the request lives (attention that sees pooled blocks of
+    the keys behind its window); each P gets a *summary group* of its own, in which a
+    request holds ``length // P`` entries.  A token's page is then kept until the token has
+    left the window AND its block's mean is taken.  ``stride`` > 1 marks such a summary
+    group's own need (made by the manager, not by mixers)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every key is kept
+    value_dim: Optional[int] = None
+    pools: Tuple[int, ...] = ()
+    stride: int = 1
 
     @property
-    def group_key(self) -> Tuple[int, int, Optional[int]]:
-        return (self.num_kv_heads, self.head_dim, self.window)
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
+
+    @property
+    def group_key(self) -> Tuple:
+        if self.value_dim is None and not self.pools and self.stride == 1:
+            return (self.num_kv_heads, self.head_dim, self.window)
+        return (self.num_kv_heads, self.head_dim, self.window, self.v_dim, self.pools,
+                self.stride)
+
+    def merged(self, other: "KVNeed") -> "KVNeed":
+        """The need of a cache that serves this execution and another that reads it: the
+        wider window, the pools of both."""
+        if (self.num_kv_heads, self.head_dim, self.v_dim) != (other.num_kv_heads,
+                                                              other.head_dim, other.v_dim):
+            raise ValueError("an execution that reads another's cache must have its head "
+                             "count and head sizes")
+        window = (None if self.window is None or other.window is None
+                  else max(self.window, other.window))
+        pools = tuple(sorted(set(self.pools) | set(other.pools))) if window is not None else ()
+        return KVNeed(self.num_kv_heads, self.head_dim, window, self.value_dim, pools)
 
 
 @dataclass(frozen=True)
@@ -93,10 +123,15 @@ def plan_pages(kv_needs: Sequence[Optional[KVNeed]], page_size: int, budget_byte
             continue
         key = need.group_key
         tokens = max_seq_len if need.window is None else min(
-            max_seq_len, need.window + max_tokens_per_step)
+            max_seq_len, need.window + max(need.pools, default=0) + max_tokens_per_step)
         per_request[key] = -(-tokens // page_size) + 2
         page_bytes[key] = page_bytes.get(key, 0) + (
-            2 * need.num_kv_heads * need.head_dim * page_size * element_size)
+            need.num_kv_heads * (need.head_dim + need.v_dim) * page_size * element_size)
+        for P in need.pools:         # the summary group of this pool size
+            sk = summary_need(need, P).group_key
+            per_request[sk] = -(-(max_seq_len // P) // page_size) + 1
+            page_bytes[sk] = page_bytes.get(sk, 0) + (
+                need.num_kv_heads * (need.head_dim + need.v_dim) * page_size * element_size)
     # pages per unit of "request": scale every group's need by the same factor f
     unit = sum(per_request[k] * page_bytes[k] for k in per_request)
     f = min(float(max_requests), budget_bytes / unit) if unit else 0.0
@@ -104,11 +139,18 @@ def plan_pages(kv_needs: Sequence[Optional[KVNeed]], page_size: int, budget_byte
     return lambda need: pages[need.group_key]
 
 
+def summary_need(need: KVNeed, pool: int) -> KVNeed:
+    """The need of the summary group that holds one mean key and value per ``pool`` tokens
+    for caches of ``need``'s geometry."""
+    return KVNeed(need.num_kv_heads, need.head_dim, None, need.value_dim, (), int(pool))
+
+
 class CacheGroup:
     def __init__(self, index: int, need: KVNeed, num_pages: int, page_size: int):
         self.index = index
         self.need = need
         self.page_size = page_size
+        self.stride = max(1, int(need.stride))   # tokens per entry (a summary group: the pool)
         # pages of one 128-key attention tile lie side by side in the pool where they can
         self.pool = PagePool(num_pages, run=max(1, 128 // page_size))
         self.entries: List[int] = []           # schedule entries stored here, in order
@@ -120,7 +162,13 @@ class CacheGroup:
         if w is None:
             return 0
         first_key = max(0, length - w + 1)
+        for P in self.need.pools:        # tokens of a block whose mean is not yet taken stay
+            first_key = min(first_key, (length // P) * P)
         return first_key // self.page_size
+
+    def entries_for(self, length: int) -> int:
+        """Entries (tokens; blocks in a summary group) that a request of ``length`` tokens holds."""
+        return length // self.stride
 
 
 class CacheManager:
@@ -139,6 +187,8 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         # schedule entry -> (group index, index of the entry inside its group)
         self.entry_location: List[Optional[Tuple[int, int]]] = []
+        # (schedule entry, pool size) -> (summary group index, index of the entry inside it)
+        self.summary_location: Dict[Tuple[int, int], Tuple[int, int]] = {}
         by_key: Dict[Tuple, CacheGroup] = {}
         for e, need in enumerate(kv_needs):
             if need is None:
@@ -151,6 +201,15 @@ class CacheManager:
                 self.groups.append(g)
             self.entry_location.append((g.index, len(g.entries)))
             g.entries.append(e)
+            for P in need.pools:
+                sn = summary_need(need, P)
+                sg = by_key.get(sn.group_key)
+                if sg is None:
+                    sg = CacheGroup(len(self.groups), sn, int(pages_of(sn)), self.page_size)
+                    by_key[sn.group_key] = sg
+                    self.groups.append(sg)
+                self.summary_location[(e, P)] = (sg.index, len(sg.entries))
+                sg.entries.append(e)
         # the largest pool (what a request that keeps every key can draw on)
         self.num_pages = max([g.pool.num_pages for g in self.groups], default=0)
         self.state_needs = list(state_needs) + [None] * (len(kv_needs) - len(state_needs))
@@ -185,7 +244,7 @@ class CacheManager:
         covered, counting the pages that the step will release first."""
         out = []
         for g, table in zip(self.groups, rc.tables):
-            want = -(-new_len // g.page_size)
+            want = -(-g.entries_for(new_len) // g.page_size)
             add = max(0, want - len(table))
             first = g.first_needed_page(rc.length)
             release = sum(1 for p in table[:first] if p > 0)
@@ -224,7 +283,7 @@ class CacheManager:
                     f"{g.pool.num_free} free of {g.pool.num_pages}")
         for g, table in zip(self.groups, rc.tables):
             self._release_passed(g, rc, table)
-            want = -(-new_len // g.page_size)
+            want = -(-g.entries_for(new_len) // g.page_size)
             while len(table) < want:
                 table.append(g.pool.alloc(after=max(table[-1], 0) if table else 0,
                                           index=len(table)))
@@ -243,7 +302,8 @@ class CacheManager:
         rc = self.requests[rid]
         assert new_len >= rc.length
         for g, table in zip(self.groups, rc.tables):
-            assert len(table) * g.page_size >= new_len, "commit beyond the reserved pages"
+            assert len(table) * g.page_size >= g.entries_for(new_len), \
+                "commit beyond the reserved pages"
         rc.length = new_len
 
     def release_passed(self, rid: Hashable) -> None:
@@ -266,7 +326,10 @@ class CacheManager:
         where a long prompt can always come in short portions."""
         for g in self.groups:
             w = g.need.window
-            need = -(-n // g.page_size) if w is None else -(-min(n, w + 1) // g.page_size) + 1
+            if w is not None:
+                w += max(g.need.pools, default=0)
+            m = g.entries_for(n)
+            need = -(-m // g.page_size) if w is None else -(-min(m, w + 1) // g.page_size) + 1
             if need > g.pool.num_pages:
                 return False
         return True
@@ -288,18 +351,24 @@ class CacheManager:
     # -------------------------------------------------------------- storage
     def allocate_storage(self, dtype, device) -> None:
         """Device tensors: per group ``[entries, 2, pages + 1, kv_heads, page_size, head_dim]``
-        (keys at index 0, values at 1; page 0 is scratch), and per schedule entry
-        with a :class:`StateNeed` a tensor ``[slots, *shape]``."""
+        (keys at index 0, values at 1; page 0 is scratch), or, where keys and values differ in
+        size, a pair of tensors ``[entries, pages + 1, kv_heads, page_size, d]``; and per
+        schedule entry with a :class:`StateNeed` a tensor ``[slots + 1, *shape]`` (the last
+        slot is scratch: padded rows of a captured step use it)."""
         import torch
         for g in self.groups:
             n = g.need
-            g.storage = torch.zeros(
-                (len(g.entries), 2, g.pool.num_pages + 1, n.num_kv_heads, g.page_size, n.head_dim),
-                dtype=dtype, device=device)
+            shape = (len(g.entries), g.pool.num_pages + 1, n.num_kv_heads, g.page_size)
+            if n.v_dim == n.head_dim:
+                g.storage = torch.zeros((shape[0], 2) + shape[1:] + (n.head_dim,),
+                                        dtype=dtype, device=device)
+            else:
+                g.storage = (torch.zeros(shape + (n.head_dim,), dtype=dtype, device=device),
+                             torch.zeros(shape + (n.v_dim,), dtype=dtype, device=device))
         for e, need in enumerate(self.state_needs):
             if need is not None:
                 self.state_storage[e] = torch.zeros(
-                    (self.slots.num_slots,) + tuple(need.shape),
+                    (self.slots.num_slots + 1,) + tuple(need.shape),
                     dtype=getattr(torch, need.dtype), device=device)
 
     def zero_fresh_state(self, rc: RequestCache) -> None:
@@ -314,12 +383,32 @@ class CacheManager:
         """(keys, values) storage of schedule entry ``entry``: each
         ``[pages + 1, kv_heads, page_size, head_dim]``; and its group index."""
         gi, ei = self.entry_location[entry]
+        return self._kv_of(gi, ei) + (gi,)
+
+    def _kv_of(self, gi: int, ei: int):
         st = self.groups[gi].storage
-        return st[ei, 0], st[ei, 1], gi
+        if isinstance(st, tuple):
+            return st[0][ei], st[1][ei]
+        return st[ei, 0], st[ei, 1]
+
+    def summary_views(self, entry: int) -> Dict[int, Tuple]:
+        """Per pool size kept for schedule entry ``entry``: (mean keys, mean values, group
+        index), each tensor ``[pages + 1, kv_heads, page_size, d]`` with one entry per block."""
+        out = {}
+        for (e, P), (gi, ei) in self.summary_location.items():
+            if e == entry:
+                out[P] = self._kv_of(gi, ei) + (gi,)
+        return out
+
+    @property
+    def scratch_slot(self) -> int:
+        """The state slot that belongs to no request."""
+        return self.slots.num_slots
 
     def storage_bytes(self) -> int:
         total = 0
         for g in self.groups:
-            if g.storage is not None:
-                total += g.storage.numel() * g.storage.element_size()
+            for st in (g.storage if isinstance(g.storage, tuple) else (g.storage,)):
+                if st is not None:
+                    total += st.numel() * st.element_size()
         return total

@@ -35,7 +35,8 @@ def registered_architectures() -> Tuple[str, ...]:
 
 
 def family_for(raw: Dict[str, Any]) -> Family:
-    archs = raw.get("architectures") or []
+    # ``architectures`` (a list, the Hugging Face spelling) or ``architecture`` (one name)
+    archs = raw.get("architectures") or raw.get("architecture") or []
     if isinstance(archs, str):
         archs = [archs]
     for a in archs:
@@ -66,6 +67,8 @@ def load_config(model_dir: str) -> Any:
 def _register_builtin() -> None:
     from .qwen3 import Qwen3Config
     register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict)
+    from .gukidra import GukidraConfig
+    register_architecture("Gukidra", GukidraConfig.from_dict)
 
 
 _register_builtin()

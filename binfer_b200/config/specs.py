@@ -28,8 +28,12 @@ class RopeSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
+    """``offset``: what is added to the stored weight to get the one that multiplies (1.0 for
+    a family whose norm weights hold the deviation from one)."""
+
     kind: str = "rmsnorm"
     eps: float = 1e-6
+    offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -81,6 +85,68 @@ class GatedMLPSpec:
     intermediate_size: int = 0
     activation: str = "silu"
     bias: bool = False
+    # the tensors' names inside the feed-forward's prefix: gate, up, down
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class PooledWindowAttentionSpec:
+    """Grouped-query attention over a window of tokens and, behind the window, one mean key
+    and value per block of ``pool`` tokens (a block is seen once all of it lies before the
+    window); keys of size ``head_dim``, values of size ``value_dim``.
+
+    ``value_rotation`` (a :class:`RopeSpec` over the whole value head): values are cached
+    turned by their own position and a head's output is turned back by the query's.
+    ``sink``: a constant logit that joins the softmax's denominator and has no value (0.0
+    adds one to the denominator); None: no sink.  ``head_gate``: each head's output is
+    multiplied by the sigmoid of a projection of the mixer's input, one number per head.
+    ``own_cache`` False: the layer reads another layer's keys and values and has no key or
+    value tensors of its own.  ``names``: the tensors inside the mixer's prefix."""
+
+    kind: str = "pooled_window_attention"
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    qk_norm: bool = True
+    qk_norm_eps: float = 1e-6
+    window: Optional[int] = None     # tokens j with p - window < j <= p; None: every token
+    pool: int = 0                    # 0: nothing behind the window is seen
+    scale: Optional[float] = None    # None = 1/sqrt(head_dim)
+    position: Optional[RopeSpec] = None
+    value_rotation: Optional[RopeSpec] = None
+    interleaved: bool = False        # pairs (2m, 2m+1) instead of (m, m + half), q, k and v alike
+    sink: Optional[float] = None
+    head_gate: bool = False
+    own_cache: bool = True
+    names: Tuple[Tuple[str, str], ...] = (
+        ("q", "q_proj.weight"), ("k", "k_proj.weight"), ("v", "v_proj.weight"),
+        ("o", "o_proj.weight"), ("g", "g_proj.weight"), ("q_norm", "q_norm.weight"),
+        ("k_norm", "k_norm.weight"))
+
+    @property
+    def softmax_scale(self) -> float:
+        return self.scale if self.scale is not None else self.head_dim ** -0.5
+
+
+@dataclass(frozen=True)
+class MLSTMSpec:
+    """A matrix memory with exponential input and forget gates per head (mLSTM), its state
+    ``S [qk_dim, v_dim]``, ``n [qk_dim]`` and a running maximum carried per request.
+    ``gate_cap`` c > 0: a gate's pre-activation z becomes ``c tanh(z / c)``.  ``norm_eps``:
+    of the per-head root mean square that divides the memory's output.  ``names``: the
+    tensors inside the mixer's prefix."""
+
+    kind: str = "mlstm"
+    num_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    gate_cap: float = 0.0
+    norm_eps: float = 1e-6
+    names: Tuple[Tuple[str, str], ...] = (
+        ("q", "q.weight"), ("k", "k.weight"), ("v", "v.weight"), ("g", "g.weight"),
+        ("o", "o.weight"), ("norm", "norm.weight"), ("i", "i.weight"), ("i_bias", "i.bias"),
+        ("f", "f.weight"), ("f_bias", "f.bias"))
 
 
 @dataclass(frozen=True)
@@ -88,7 +154,8 @@ class LayerSpec:
     """One decoder layer: which mixer, which feed-forward, which norm, how arranged."""
 
     mixer: object = None         # a mixer spec with a ``kind`` attribute
-    ffn: object = None           # a feed-forward spec with a ``kind`` attribute
+    ffn: object = None           # a feed-forward spec with a ``kind`` attribute (None: the
+                                 # arrangement has no second sublayer in this layer)
     norm: NormSpec = NormSpec()
     block: str = "prenorm"       # arrangement of the parts inside the layer
 
@@ -142,6 +209,8 @@ class NameLayout:
     ffn: str = "mlp"
     final_norm: str = "model.norm.weight"
     lm_head: str = "lm_head.weight"
+    # what follows a layer norm's name to give its tensor's name
+    norm_suffix: str = ".weight"
     # further norms of a layer, for arrangements that have more than the two above:
     # (role, name inside the layer) pairs
     more_norms: Tuple[Tuple[str, str], ...] = ()

@@ -393,6 +393,156 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
          _c_float(scale), _ptr(err), _stream())
 
 
+# ----------------------------------------------------- norm on a sublayer's output
+def rmsnorm_add(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor,
+                reading: Optional[torch.Tensor], eps: float) -> None:
+    """``resid += y * rsqrt(mean(y^2) + eps) * weight`` row by row (``resid`` float32
+    ``[T, H]``), and, if ``reading`` is given, the new rows in its type."""
+    _want(resid, torch.float32, "resid"); _want(weight, torch.float32, "weight")
+    T, H = resid.shape
+    if y.shape != resid.shape or not y.is_contiguous():
+        raise KernelError("rmsnorm_add: y must be contiguous and of the stream's shape")
+    if reading is not None and (reading.dtype != y.dtype or reading.shape != resid.shape
+                                or not reading.is_contiguous()):
+        raise KernelError("rmsnorm_add: the reading must be contiguous, of y's type and shape")
+    _run("rmsnorm_add", lib().bf_rmsnorm_add, _ptr(resid), _ptr(y), _ptr(weight), _ptr(reading),
+         _c_int(T), _c_int(H), _c_float(eps), _c_int(_dtype_code(y)), _stream())
+
+
+def stream_to_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
+    _want(x, torch.float32, "x"); _want(out, torch.bfloat16, "out")
+    _run("stream_to_bf16", lib().bf_stream_to_bf16, _ptr(x), _ptr(out), _c_ll(x.numel()),
+         _stream())
+
+
+# ------------------------------------------------------------------ matrix memory (mLSTM)
+def mlstm_gates(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                gates: torch.Tensor, heads: int, cap: float) -> None:
+    """``gates [T, 2 heads]`` float32 from ``h [T, width]`` and ``w [2 heads, width]`` (input
+    gate rows, then forget gate rows): the capped pre-activation for an input gate, its
+    log-sigmoid for a forget gate."""
+    T, width = h.shape
+    if h.stride(1) != 1 or w.shape != (2 * heads, width) or not w.is_contiguous() \
+            or w.dtype != h.dtype:
+        raise KernelError("mlstm_gates: w must be contiguous [2 heads, width] of h's type")
+    _want(gates, torch.float32, "gates")
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+    _run("mlstm_gates", lib().bf_mlstm_gates, _ptr(h), _c_ll(h.stride(0)), _ptr(w), _ptr(bias),
+         _ptr(gates), _c_int(T), _c_int(width), _c_int(heads), _c_float(cap),
+         _c_int(_dtype_code(h)), _stream())
+
+
+MLSTM_MAX_QK_DIM = 256
+
+
+def mlstm_state_size(dk: int, dv: int) -> int:
+    """Floats of one head's state: S, n, m and padding to a multiple of four."""
+    return dk * dv + dk + 4
+
+
+def mlstm_scan(proj: torch.Tensor, gates: torch.Tensor, state: torch.Tensor,
+               q_start: torch.Tensor, state_slots: torch.Tensor, o_raw: torch.Tensor, B: int,
+               heads: int, dk: int, dv: int, q_scale: float, err: torch.Tensor) -> None:
+    """The recurrence over every request's tokens of this step.  ``proj`` rows hold
+    ``[q: heads dk | k: heads dk | v: heads dv | ...]``; ``state`` is float32
+    ``[slots, heads, mlstm_state_size]``; ``o_raw`` float32 ``[T, heads dv]`` receives the
+    memory's output before its norm and gate."""
+    _want(gates, torch.float32, "gates"); _want(state, torch.float32, "state")
+    _want(o_raw, torch.float32, "o_raw")
+    if proj.stride(1) != 1 or dk > MLSTM_MAX_QK_DIM:
+        raise KernelError(f"mlstm_scan: contiguous rows and a key size of at most "
+                          f"{MLSTM_MAX_QK_DIM}")
+    if state.shape[1:] != (heads, mlstm_state_size(dk, dv)):
+        raise KernelError("mlstm_scan: state must be [slots, heads, mlstm_state_size(dk, dv)]")
+    _run("mlstm_scan", lib().bf_mlstm_scan, _ptr(proj), _c_ll(proj.stride(0)), _ptr(gates),
+         _ptr(state), _c_ll(state.stride(0)), _c_int(state.shape[2]), _ptr(q_start),
+         _ptr(state_slots), _c_int(state.shape[0]), _ptr(o_raw), _c_int(B), _c_int(heads),
+         _c_int(dk), _c_int(dv), _c_float(q_scale), _c_int(_dtype_code(proj)), _ptr(err),
+         _stream())
+
+
+def mlstm_out(o_raw: torch.Tensor, proj: torch.Tensor, g_off: int, norm_w: torch.Tensor,
+              out: torch.Tensor, heads: int, dv: int, eps: float) -> None:
+    """``out = o_raw / rms_per_head(o_raw) * norm_w * sigmoid(proj[:, g_off:])``."""
+    _want(o_raw, torch.float32, "o_raw"); _want(norm_w, torch.float32, "norm_w")
+    T = o_raw.shape[0]
+    if not out.is_contiguous() or out.dtype != proj.dtype:
+        raise KernelError("mlstm_out: out must be contiguous and of the projection's type")
+    _run("mlstm_out", lib().bf_mlstm_out, _ptr(o_raw), _ptr(proj), _c_ll(proj.stride(0)),
+         _c_ll(g_off), _ptr(norm_w), _ptr(out), _c_int(T), _c_int(heads), _c_int(dv),
+         _c_float(eps), _c_int(_dtype_code(proj)), _stream())
+
+
+# ------------------------------------------- windowed attention with pooled blocks
+def apw_encode(proj: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+               inv_freq: Optional[torch.Tensor], v_inv_freq: Optional[torch.Tensor],
+               interleaved: bool, positions: torch.Tensor, slots: Optional[torch.Tensor],
+               q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+               v_cache: Optional[torch.Tensor], nh: int, nkv: int, dk: int, dv: int,
+               eps: float, err: torch.Tensor) -> None:
+    """Head norms and rotation of q and k, rotation of v over its whole head; q to
+    ``q_out [T, nh dk]``, k and v into their pages at ``slots``.  Without caches only the
+    queries are taken (``proj`` rows then need hold nothing else at their start)."""
+    T = proj.shape[0]
+    if proj.stride(1) != 1:
+        raise KernelError("apw_encode: rows must be contiguous")
+    writes = k_cache is not None
+    if writes and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError("cache pages must be contiguous")
+    page_size = k_cache.shape[2] if writes else 1
+    num_slots = k_cache.shape[0] * page_size if writes else 0
+    _run("apw_encode", lib().bf_apw_encode, _ptr(proj), _c_ll(proj.stride(0)), _ptr(q_w),
+         _ptr(k_w), _ptr(inv_freq), _c_int(0 if inv_freq is None else inv_freq.numel()),
+         _ptr(v_inv_freq), _c_int(1 if interleaved else 0), _ptr(positions),
+         _ptr(slots if writes else None), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _c_int(T),
+         _c_int(nh), _c_int(nkv if writes else 0), _c_int(dk), _c_int(dv), _c_int(page_size),
+         _c_ll(num_slots), _c_float(eps), _c_int(_dtype_code(proj)), _ptr(err), _stream())
+
+
+def apw_pool_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, ks_cache: torch.Tensor,
+                    vs_cache: torch.Tensor, q_start: torch.Tensor, ctx_lens: torch.Tensor,
+                    tables: torch.Tensor, s_tables: torch.Tensor, B: int, max_new_blocks: int,
+                    nkv: int, dk: int, dv: int, pool: int, err: torch.Tensor) -> None:
+    """Mean key and value of every block of ``pool`` tokens that this step completed, into
+    the summary pages (entry ``block`` of the request's summary table)."""
+    _run("apw_pool_blocks", lib().bf_apw_pool_blocks, _ptr(k_cache), _ptr(v_cache),
+         _ptr(ks_cache), _ptr(vs_cache), _ptr(q_start), _ptr(ctx_lens), _ptr(tables),
+         _c_int(tables.stride(0)), _ptr(s_tables), _c_int(s_tables.stride(0)), _c_int(B),
+         _c_int(max_new_blocks), _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(k_cache.shape[2]),
+         _c_int(k_cache.shape[0]), _c_int(ks_cache.shape[2]), _c_int(ks_cache.shape[0]),
+         _c_int(pool), _c_int(_dtype_code(k_cache)), _ptr(err), _stream())
+
+
+def apw_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  ks_cache: Optional[torch.Tensor], vs_cache: Optional[torch.Tensor],
+                  seq_of_token: torch.Tensor, positions: torch.Tensor, tables: torch.Tensor,
+                  s_tables: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                  v_inv_freq: Optional[torch.Tensor], interleaved: bool, out: torch.Tensor,
+                  nh: int, nkv: int, dk: int, dv: int, window: Optional[int], pool: int,
+                  scale: float, sink: Optional[float], err: torch.Tensor) -> None:
+    """Attention of every token row over the window's tokens and the pooled blocks behind
+    it (one softmax, ``exp(sink)`` in its denominator if a sink is given), the head's output
+    turned back by the row's position (``v_inv_freq``) and multiplied by the sigmoid of
+    ``gate[t, h]`` (a strided view ``[T, nh]``).  Any sizes: values up to 256 a head."""
+    T = q.shape[0]
+    if not q.is_contiguous() or not out.is_contiguous():
+        raise KernelError("apw_attention: q and out must be contiguous")
+    if gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise KernelError("apw_attention: gate rows must be contiguous and of q's type")
+    has_s = ks_cache is not None
+    _run("apw_attention", lib().bf_apw_attention, _ptr(q), _ptr(k_cache), _ptr(v_cache),
+         _ptr(ks_cache), _ptr(vs_cache), _ptr(seq_of_token), _ptr(positions), _ptr(tables),
+         _c_int(tables.stride(0)), _ptr(s_tables), _c_int(s_tables.stride(0) if has_s else 0),
+         _ptr(gate), _c_ll(gate.stride(0) if gate is not None else 0), _ptr(v_inv_freq),
+         _c_int(1 if interleaved else 0), _ptr(out), _c_int(T), _c_int(nh), _c_int(nkv),
+         _c_int(dk), _c_int(dv), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
+         _c_int(ks_cache.shape[2] if has_s else 1), _c_int(ks_cache.shape[0] if has_s else 0),
+         _c_int(window or 0), _c_int(pool if has_s else 0), _c_float(scale),
+         _c_int(0 if sink is None else 1), _c_float(sink or 0.0), _c_int(_dtype_code(q)),
+         _ptr(err), _stream())
+
+
 # ------------------------------------------------------------- matrix products
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic."""

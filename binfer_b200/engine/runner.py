@@ -185,6 +185,7 @@ class ModelRunner:
             rows[:] = np.arange(B, dtype=np.int32)
         view("ctx_lens")[:] = ctx_lens
         view("state_slots")[:n_real] = [rc.slot for rc in rcs]
+        view("state_slots")[n_real:] = cache.scratch_slot     # padded rows own no state
         for g in cache.groups:
             gi, w, ps = g.index, widths[g.index], g.page_size
             sl = view(f"slots{gi}")
@@ -197,7 +198,11 @@ class ModelRunner:
                                      f"block table has room for {w}")
                 tb[b, :len(table)] = table
                 n, start = q_lens[b], starts[b]
-                if n == 1:
+                if g.stride > 1:
+                    # a summary group holds an entry per block, written by the kernel that
+                    # takes the means; no token has a place of its own in it
+                    sl[t:t + n] = -1
+                elif n == 1:
                     sl[t] = int(table[start // ps]) * ps + start % ps
                 else:
                     p = np.arange(start, start + n)

@@ -141,6 +141,11 @@ class Norm(Part):
                 n_rows: int = 0) -> torch.Tensor:
         raise NotImplementedError
 
+    def add_normed(self, stream: "ResidualStream", y: torch.Tensor) -> None:
+        """``stream += norm(y)``: the norm on a sublayer's output (arrangements whose
+        sublayers read the stream itself).  Leaves ``stream.reading`` current."""
+        raise NotImplementedError
+
 
 @dataclass
 class EntryView:
@@ -151,7 +156,10 @@ class EntryView:
     k_cache: Optional[torch.Tensor]    # [pages + 1, kv_heads, page_size, head_dim]
     v_cache: Optional[torch.Tensor]
     writes_cache: bool                 # False when the pages belong to another entry
-    state: Optional[torch.Tensor]      # [slots, *shape] of the mixer's StateNeed
+    state: Optional[torch.Tensor]      # [slots + 1, *shape] of the mixer's StateNeed
+    # pool size -> (mean keys, mean values, cache group): one entry per block of that many
+    # tokens, for attention that sees pooled blocks behind its window
+    summaries: Dict[int, tuple] = field(default_factory=dict)
 
 
 class DeferredLinear:
@@ -203,12 +211,28 @@ class ResidualStream:
         self.pending: Optional[torch.Tensor] = None
         self.ready: Optional[ScaledRows] = None
         self.ready_for = None
+        # the stream itself in the activation type, for sublayers that read it without a
+        # norm in front; kept by the kernel that last changed the stream, dropped by any other
+        self.reading: Optional[torch.Tensor] = None
 
     def add(self, delta: torch.Tensor) -> None:
         if self.pending is not None:
             self.flush()
         self.pending = delta
         self.ready = self.ready_for = None
+        self.reading = None
+
+    def read(self, dtype: torch.dtype) -> torch.Tensor:
+        """The stream as a sublayer's products take it: itself in a float engine, else a copy
+        in ``dtype`` (made here unless the last add left one)."""
+        self.flush()
+        if dtype == torch.float32:
+            return self.x
+        if self.reading is None or self.reading.dtype != dtype:
+            from ..csrc import ops
+            self.reading = torch.empty(self.x.shape, dtype=dtype, device=self.x.device)
+            ops.stream_to_bf16(self.x, self.reading)
+        return self.reading
 
     def add_linear(self, d: DeferredLinear, norm=None, consumer=None) -> None:
         """Add ``d.x @ d.w^T``.  ``norm`` is the norm that reads the stream next and
@@ -217,6 +241,7 @@ class ResidualStream:
         :class:`ScaledRows`."""
         from .linear import linear_add_norm
         fs = getattr(norm, "fused_scale", None)
+        self.reading = None
         if fs is not None and getattr(consumer, "accepts_scaled_rows", False):
             self.flush()
             weight, eps = fs()

@@ -38,9 +38,10 @@ class GatedMLP(FeedForward):
 
     def param_specs(self) -> List[ParamSpec]:
         p = self.prefix
-        return [ParamSpec(p + "gate_proj.weight", (self.inter, self.hidden)),
-                ParamSpec(p + "up_proj.weight", (self.inter, self.hidden)),
-                ParamSpec(p + "down_proj.weight", (self.hidden, self.inter))]
+        gate, up, down = self.spec.names
+        return [ParamSpec(p + gate, (self.inter, self.hidden)),
+                ParamSpec(p + up, (self.inter, self.hidden)),
+                ParamSpec(p + down, (self.hidden, self.inter))]
 
     def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
         g, u, d = self.param_specs()

@@ -25,7 +25,10 @@ from .linear import linear
 
 # importing the modules registers the built-in parts
 from . import attention as _attention  # noqa: F401
+from . import attention_pooled as _attention_pooled  # noqa: F401
 from . import block as _block          # noqa: F401
+from . import block_sublayer_norm as _block_sublayer_norm  # noqa: F401
+from . import mlstm as _mlstm          # noqa: F401
 from . import mlp as _mlp              # noqa: F401
 from . import norms as _norms          # noqa: F401
 from . import rope as _rope            # noqa: F401
@@ -97,6 +100,13 @@ class DecoderModel:
         for entry in self.spec.schedule:
             need = self.blocks[entry.layer].mixer.kv_need()
             out.append(need if entry.cache_from is None else None)
+        # an execution that reads another's pages may look further back, or at pooled blocks
+        # of another size: the pages are kept for the widest of them
+        for entry in self.spec.schedule:
+            if entry.cache_from is not None and out[entry.cache_from] is not None:
+                need = self.blocks[entry.layer].mixer.kv_need()
+                if need is not None and need != out[entry.cache_from]:
+                    out[entry.cache_from] = out[entry.cache_from].merged(need)
         return out
 
     def state_needs(self) -> List[Optional[StateNeed]]:
@@ -110,7 +120,8 @@ class DecoderModel:
                 k = v = g = None
             else:
                 k, v, g = cache.kv_view(src)
-            views.append(EntryView(e, g, k, v, entry.cache_from is None, cache.state_storage[e]))
+            views.append(EntryView(e, g, k, v, entry.cache_from is None, cache.state_storage[e],
+                                   summaries=cache.summary_views(src)))
         return views
 
     # ----------------------------------------------------------------- forward

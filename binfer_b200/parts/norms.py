@@ -20,16 +20,21 @@ from .base import BuildEnv, Norm, ResidualStream, register_norm
 class RMSNorm(Norm):
     def __init__(self, spec: NormSpec, size: int, name: str, env: BuildEnv):
         self.eps = float(spec.eps)
+        self.offset = float(getattr(spec, "offset", 0.0))
         self.size = size
         self.name = name
         self.env = env
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec(self.name, (self.size,), init="norm", role="vector")]
+        init = "around_zero" if self.offset else "norm"
+        return [ParamSpec(self.name, (self.size,), init=init, role="vector")]
 
     def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
         self.weight = get(self.param_specs()[0])
+        if self.offset:
+            # the weight that multiplies is offset + what the checkpoint holds, in float
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
                 n_rows: int = 0) -> torch.Tensor:
@@ -48,6 +53,20 @@ class RMSNorm(Norm):
             stream.pending = None
         return out
 
+
+    def add_normed(self, stream: ResidualStream, y: torch.Tensor) -> None:
+        """``stream.x += y * rsqrt(mean(y^2) + eps) * w`` in one kernel, which also leaves the
+        new stream in the activation type for the next sublayer's products."""
+        stream.flush()
+        stream.ready = stream.ready_for = None
+        if y.dtype != self.env.dtype or y.shape != stream.x.shape:
+            raise ValueError("add_normed: the sublayer's output must have the stream's shape "
+                             "and the engine's activation type")
+        reading = None
+        if self.env.dtype != torch.float32:
+            reading = torch.empty(stream.x.shape, dtype=self.env.dtype, device=self.env.device)
+        ops.rmsnorm_add(stream.x, y, self.weight, reading, self.eps)
+        stream.reading = reading
 
     def fused_scale(self):
         """(weight, eps): what a product needs to prepare this norm in its epilogue."""

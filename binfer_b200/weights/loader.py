@@ -33,7 +33,8 @@ class ParamSpec:
 
     name: str
     shape: Tuple[int, ...]
-    # how the random-weights mode fills it: "matrix" ~ N(0, s), "norm" ~ 1 + N(0, s_norm)
+    # how the random-weights mode fills it: "matrix" ~ N(0, s), "norm" ~ 1 + N(0, s_norm),
+    # "around_zero" ~ N(0, s_norm), "zeros"
     init: str = "matrix"
     # a matrix feeds a matrix product and takes the engine's compute dtype;
     # a vector (norm weight, bias) is held in 32-bit whatever it was stored in

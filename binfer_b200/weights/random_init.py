@@ -25,7 +25,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(spec: ParamSpec, seed: int, std: float, norm_std: float,
                   dtype: torch.dtype = torch.float32,
                   device: torch.device | str = "cpu") -> torch.Tensor:
-    """``matrix``: N(0, std).  ``norm``: 1 + N(0, norm_std).  ``zeros``: 0."""
+    """``matrix``: N(0, std).  ``norm``: 1 + N(0, norm_std).  ``around_zero``: N(0, norm_std).
+    ``zeros``: 0."""
     device = torch.device(device)
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, spec.name))
@@ -42,6 +43,8 @@ def random_tensor(spec: ParamSpec, seed: int, std: float, norm_std: float,
         x.normal_(0.0, 1.0, generator=g)
     if spec.init == "norm":
         x.mul_(norm_std).add_(1.0)
+    elif spec.init == "around_zero":
+        x.mul_(norm_std)
     else:
         x.mul_(std)
     return x.to(dtype)
