@@ -74,7 +74,9 @@ class ModelRunner:
         if env.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only (there is no CPU path)")
         self.model, self.cache, self.env = model, cache, env
-        if any(g.storage is None for g in cache.groups):
+        if any(g.storage is None for g in cache.groups) or any(
+                need is not None and st is None
+                for need, st in zip(cache.state_needs, cache.state_storage)):
             cache.allocate_storage(env.dtype, env.device)
         self.views = model.entry_views(cache)
         from ..csrc import ops

@@ -283,3 +283,89 @@ def run_trace(runner, steps: List[dict]) -> Dict[Tuple[str, int], torch.Tensor]:
             del pos[rid]
         runner.cache.check_consistent()
     return out
+
+
+# ------------------------------------------------------------------ the hybrid design
+def _guk_attn(heads, kv_heads, dim, vdim, window, pool, rot_dims, base=10000.0, scale=None,
+              kv_from=None, layout=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+         "mask": {"size": window, "pool": pool},
+         "rot": {"base": base, "dims": rot_dims},
+         "scale": dim ** -0.5 if scale is None else scale}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    if layout is not None:
+        m["rot"]["layout"] = layout
+    return m
+
+
+def _guk_layer(kind, mixer, ff=None):
+    return {"type": kind, "mixer": mixer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def _guk_mlstm(heads, dim, vdim, cap):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}
+
+
+# memory / attention alternating; a memory layer with a feed-forward, an attention layer
+# without; the second attention layer reads the first one's keys and values
+GUK_A = {"architecture": "Gukidra", "vocab": 300, "width": 64, "norm": {"eps": 1e-6},
+         "embedding": {"scale": 6.0},
+         "layers": [_guk_layer("mlstm", _guk_mlstm(2, 16, 32, 8.0)),
+                    _guk_layer("attention", _guk_attn(4, 2, 32, 16, 24, 4, 16), ff=96),
+                    _guk_layer("mlstm", _guk_mlstm(2, 16, 32, 8.0), ff=80),
+                    _guk_layer("attention", _guk_attn(4, 2, 32, 16, 24, 4, 16, kv_from=1))]}
+# attention first; no grouping; values larger than keys and no multiple of 32; a window
+# smaller than the pooled block; the reader has a mask of its own (wider window, other block);
+# one memory head; no embedding scale
+GUK_B = {"architecture": "Gukidra", "vocab": 211, "width": 48, "norm": {"eps": 1e-5},
+         "embedding": {"scale": 1.0},
+         "layers": [_guk_layer("attention", _guk_attn(3, 3, 24, 40, 7, 8, 24, base=500.0, scale=0.3),
+                               ff=64),
+                    _guk_layer("mlstm", _guk_mlstm(1, 40, 24, 5.0)),
+                    _guk_layer("attention", _guk_attn(3, 3, 24, 40, 20, 5, 24, base=500.0,
+                                                      scale=0.25, kv_from=0), ff=72),
+                    _guk_layer("mlstm", _guk_mlstm(3, 8, 8, 15.0), ff=56)]}
+# a window of one token and blocks of one token: every earlier token is seen as a block;
+# one key/value head; interleaved pairs
+GUK_C = {"architecture": "Gukidra", "vocab": 150, "width": 32, "norm": {"eps": 1e-6},
+         "embedding": {"scale": 3.0},
+         "layers": [_guk_layer("attention", _guk_attn(2, 1, 16, 16, 1, 1, 8, layout="interleaved"),
+                               ff=48),
+                    _guk_layer("mlstm", _guk_mlstm(2, 8, 16, 10.0)),
+                    _guk_layer("attention", _guk_attn(2, 1, 16, 16, 5, 3, 16), ff=40)]}
+# wider, for bfloat16: heads of 64 and 128, a window of 64 with blocks of 16
+GUK_D = {"architecture": "Gukidra", "vocab": 500, "width": 256, "norm": {"eps": 1e-6},
+         "embedding": {"scale": 10.0},
+         "layers": [_guk_layer("mlstm", _guk_mlstm(4, 64, 64, 12.0)),
+                    _guk_layer("attention", _guk_attn(4, 1, 64, 128, 64, 16, 32), ff=512),
+                    _guk_layer("mlstm", _guk_mlstm(2, 32, 128, 12.0)),
+                    _guk_layer("attention", _guk_attn(4, 1, 64, 128, 64, 16, 32, kv_from=1),
+                               ff=384)]}
+
+GUK = {
+    "A": dict(raw=GUK_A, std=0.08, norm_std=0.1, page_size=16, seed=5),
+    "B": dict(raw=GUK_B, std=0.1, norm_std=0.1, page_size=4, seed=6),
+    "C": dict(raw=GUK_C, std=0.12, norm_std=0.1, page_size=8, seed=7),
+    "D": dict(raw=GUK_D, std=0.05, norm_std=0.05, page_size=16, seed=8),
+}
+
+
+def make_gukidra_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None, tag="") -> str:
+    """A folder with config.json and random weights of a hybrid configuration; ``tweak(w)``
+    may change the tensors (a name -> tensor dictionary) before they are written."""
+    from binfer_b200.config import GukidraConfig
+    from binfer_b200.parts.model import param_specs_for
+    from binfer_b200.weights import random_tensors, save_file
+    t = GUK[which]
+    raw = raw or t["raw"]
+    cfg = GukidraConfig.from_dict(raw)
+    d = os.path.join(str(tmp_path), f"guk_{which}{tag}_{str(dtype).split('.')[-1]}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    w = random_tensors(param_specs_for(cfg.to_spec()), t["seed"], t["std"], t["norm_std"], dtype)
+    if tweak is not None:
+        tweak(w)
+    save_file(w, os.path.join(d, "model.safetensors"))
+    return d

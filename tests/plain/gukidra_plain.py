@@ -197,3 +197,15 @@ def forward(raw: dict, w: Dict[str, torch.Tensor], tokens: List[int],
         if layers_out is not None:
             layers_out.append(x.clone())
     return unit_offset_rms_norm(x, w["final.norm"], eps) @ w["embed"].T
+
+
+def greedy_generate(raw: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int,
+                    dtype: torch.dtype = torch.float64) -> List[int]:
+    """``n`` tokens after ``prompt``, each the largest logit's (the lowest id on a tie); the
+    whole sequence is run again for every token."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        row = forward(raw, w, toks, dtype)[-1]
+        out.append(int(torch.argmax(row)))
+        toks.append(out[-1])
+    return out
