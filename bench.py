@@ -248,6 +248,117 @@ def serve_point(peaks, layers=None, page_size=PAGE_SIZE):
     return r
 
 
+# ------------------------------------------------------------- the hybrid design beside Qwen3
+# name -> (width, attention heads, kv heads, head size, feed-forward, memory heads, memory key
+# size, memory value size): the attention and feed-forward sizes of the Qwen3 shape of that
+# name; the matrix memory's sizes follow the published xLSTM models (keys half, values all of
+# the width over its heads)
+HYBRID_SIZES = {"1.7b": (2048, 16, 8, 128, 6144, 4, 256, 512),
+                "8b": (4096, 32, 8, 128, 12288, 8, 256, 512)}
+
+
+def hybrid_config(size, layers, window=1024, pool=16):
+    width, heads, kv, d, ff, mh, mdk, mdv = HYBRID_SIZES[size]
+    attn = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5,
+            "mask": {"size": window, "pool": pool}, "rot": {"base": 1e6, "dims": d}}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "mlstm", "mlp": None,
+                        "mixer": {"heads": mh, "dim": mdk, "vdim": mdv, "gate_cap": 15.0}})
+        else:
+            mixer = dict(attn, kv_from=i - 2) if i % 4 == 3 else dict(attn)
+            out.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Gukidra", "vocab": 32000, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 8.0}, "layers": out}
+
+
+def hybrid_compare(args):
+    """Prefill and decode throughput of the hybrid design (matrix-memory layers alternating
+    with pooled-window attention layers) at layer sizes of real models, beside the Qwen3
+    decoder of the same width, heads, feed-forward and layer count: one prompt of 2,048
+    tokens in one step, and decode steps at --batch (8) requests with 4,096 tokens of context
+    (CUDA graphs), each timed with CUDA events after warm-up; then per-kernel times of both
+    (event pairs around every launch, eager).  Random weights, bfloat16."""
+    import torch
+    from binfer_b200 import Engine, Qwen3Config
+    from binfer_b200.config import GukidraConfig
+    from binfer_b200.engine.runner import StepItem
+    from binfer_b200.profiling import Profiler
+    layers = args.layers or 8
+    B, context, ps = args.batch or 8, 4096, args.page_size
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+    record = {"metric": "hybrid design beside the Qwen3 decoder at equal layer sizes "
+                        "(prefill of 2048 tokens; decode at batch %d, context %d)" % (B, context),
+              "dtype": "bf16", "data": "synthetic", "layers": layers, "sizes": {}}
+    for size in (args.hybrid_sizes.split(",") if args.hybrid_sizes else sorted(HYBRID_SIZES)):
+        width, heads, kv, d, ff = HYBRID_SIZES[size][:5]
+        qwen = dict(SHAPES[size][0], num_hidden_layers=layers, vocab_size=32000,
+                    tie_word_embeddings=True)
+        out = {}
+        for name, cfg in (("hybrid", GukidraConfig.from_dict(hybrid_config(size, layers))),
+                          ("qwen3", Qwen3Config.from_dict(qwen))):
+            engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=(B + 1) * (context // ps) + 64,
+                            page_size=ps, max_seq_len=context, max_batch_size=B + 1,
+                            max_tokens_per_step=2048, cuda_graphs=True)
+            runner = engine.runner
+            gen = torch.Generator().manual_seed(0)
+            vocab = engine.spec.vocab_size
+            toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+
+            def prefill():
+                runner.add_request("pf")
+                runner.step([StepItem("pf", toks, [PREFILL_TOKENS - 1])])
+                runner.free_request("pf")
+
+            def timed(fn, n, w):
+                for _ in range(w):
+                    fn()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(n):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b) / n
+
+            pf_ms = timed(prefill, 5, 3)
+            rids = fill_cache(engine, runner, B, context - (steps + warmup) - 8, vocab, gen)
+            k = [0]
+
+            def decode():
+                k[0] += 1
+                runner.step([StepItem(r, [(7 * k[0] + i) % vocab], [0]) for i, r in enumerate(rids)])
+
+            dec_ms = timed(decode, steps, warmup)
+            runner.check_errors()
+            res = {"prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / pf_ms * 1e3),
+                   "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(B / dec_ms * 1e3),
+                   "weight_gb": round(engine.model.weight_bytes() / 1e9, 3)}
+            # per-kernel shares, eager: the decode step of requests that are freed afterwards
+            runner._buckets = None
+            kernels = {}
+            for what, fn in (("prefill", prefill), ("decode", decode)):
+                fn(); fn()
+                torch.cuda.synchronize()
+                prof = Profiler()
+                for _ in range(3):
+                    fn()
+                prof.stop()
+                kernels[what] = {kn: [c // 3, round(ms / 3, 4)] for kn, (c, ms) in
+                                 sorted(prof.collect().items(), key=lambda kv: -kv[1][1])}
+            res["kernels_calls_ms"] = kernels
+            out[name] = res
+            for r in rids:
+                runner.free_request(r)
+            del engine, runner
+            torch.cuda.empty_cache()
+        record["sizes"][size] = out
+    print(json.dumps(record))
+    return 0
+
+
 def profile_steps(args):
     """Per-kernel time of one prefill step and of one decode step, eager (event pairs around
     every launch: short kernels read longer than inside a captured step, so shares, not
@@ -320,6 +431,11 @@ def main():
                     help="instead of the bench line: per-kernel CUDA events of a prefill of 2,048 "
                          "tokens and of a decode step at --batch (eager launches; the "
                          "reference's spans: src/profiler/profiler.ts:93-479)")
+    ap.add_argument("--hybrid", action="store_true",
+                    help="instead of the bench line: prefill and decode throughput of the hybrid "
+                         "design (matrix memory + pooled-window attention) beside the Qwen3 "
+                         "decoder at equal layer sizes, with per-kernel times")
+    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid: 1.7b, 8b or both (default)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -328,6 +444,8 @@ def main():
         return 2
     args.warmup = max(args.warmup, 3)
     peaks = load_peaks()
+    if args.hybrid:
+        return hybrid_compare(args)
     if args.profile:
         return profile_steps(args)
     if args.workload == "serve":

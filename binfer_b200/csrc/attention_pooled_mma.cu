@@ -1,0 +1,388 @@
+// Windowed attention with pooled blocks (see attention_pooled.cu for what it computes) on the
+// tensor cores, bfloat16, for prompt portions and single tokens alike.
+//
+// A CTA of four warps takes 64 *rows* of one request and one key/value head: a row is a
+// (token, query head of the group) pair, tokens in order and the group's heads side by side,
+// so one tile of keys and values serves every head that shares it.  The CTA walks first the
+// pooled blocks that its last row sees (64 block means a tile), then the tokens from the
+// first row's window start to the last row's position (64 keys a tile, tile edges at
+// multiples of 64).  Per tile: K and V rows come through the block table into shared
+// memory, S = Q K^T by mma.sync m16n8k16 (Q fragments stay in registers), each row masks by
+// its own position (a block is seen if it lies wholly before the row's window; a token if it
+// is inside it), online softmax in float in base 2, P in bfloat16 straight from the
+// accumulators into the A fragments of O += P V.  The epilogue adds the sink to the
+// denominator, turns the head's output back by the row's position (values are cached
+// turned by theirs), multiplies by the head's gate and stores.
+//
+// Key and value head sizes: multiples of 16 up to 128; at most 64 query heads per kv head.
+#include <float.h>
+
+#include "common.cuh"
+
+#define PWM_ROWS 64
+#define PWM_KEYS 64
+#define PWM_THREADS 128
+
+__device__ __forceinline__ void pwm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void pwm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void pwm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pwm_pack(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void pwm_cp16(void* smem, const void* gmem, bool valid) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;              // 0: nothing is read, the 16 bytes are zeroed
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void pwm_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N>
+__device__ __forceinline__ void pwm_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+// Which pieces (16 bytes each) of a 64-row tile a thread copies: row and column of each of
+// its at most eight pieces, worked out once (row in the low byte, column above; -1: none).
+struct PwmPieces {
+  int rc[8];
+};
+__device__ __forceinline__ PwmPieces pwm_pieces(int d) {
+  PwmPieces p;
+  const int chunks = d >> 3, total = PWM_KEYS * chunks;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = threadIdx.x + PWM_THREADS * k;
+    const int r = i / chunks;
+    p.rc[k] = i < total ? (r | (((i - r * chunks) << 3) << 8)) : -1;
+  }
+  return p;
+}
+
+// Rows `first .. first + 63` (entries of a paged cache, through `table`) on their way into a
+// shared tile of `d` columns and `pitch` elements a row, by asynchronous 16-byte copies; rows
+// before `lo` or at or beyond `limit` are zeroed (their pages may be gone).  The pages of a
+// thread's pieces are looked up first, all at once, so that the lookups' round trips overlap.
+// `ps_shift`: log2 of the page size, or -1 if that is no power of two.
+__device__ __forceinline__ void pwm_load_tile(__nv_bfloat16* tile, int pitch, const PwmPieces& pc,
+                                              const __nv_bfloat16* __restrict__ cache,
+                                              const int* __restrict__ table, int first, int lo,
+                                              int limit, int d, int nkv, int g, int page_size,
+                                              int ps_shift, int num_pages,
+                                              int* __restrict__ err) {
+  int pages[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int e = first + (pc.rc[k] & 255);
+    const bool want = pc.rc[k] >= 0 && e >= lo && e < limit;
+    pages[k] = want ? table[ps_shift >= 0 ? e >> ps_shift : e / page_size] : -2;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (pc.rc[k] >= 0) {
+      const int r = pc.rc[k] & 255, c = pc.rc[k] >> 8;
+      const int e = first + r;
+      const int page = pages[k];
+      const bool ok = page >= 0 && page < num_pages;
+      if (!ok && page != -2) atomicOr(err, BF_ERR_PAGE);
+      const int off = ps_shift >= 0 ? e & (page_size - 1) : e % page_size;
+      const __nv_bfloat16* src =
+          ok ? cache + (((size_t)page * nkv + g) * page_size + off) * d + c : cache;
+      pwm_cp16(tile + (size_t)r * pitch + c, src, ok);
+    }
+  }
+}
+
+template <int DKS, int DVT>          // key size <= 16 DKS, value size <= 8 DVT
+__global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+    const __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ ks_cache,
+    const __nv_bfloat16* __restrict__ vs_cache, const int* __restrict__ q_start,
+    const int* __restrict__ positions, const int* __restrict__ tables, int table_stride,
+    const int* __restrict__ s_tables, int s_table_stride, const __nv_bfloat16* __restrict__ gate,
+    long long gate_stride, const float* __restrict__ v_inv_freq, int interleaved,
+    __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
+    int num_pages, int s_page_size, int s_num_pages, int window, int pool, float scale_log2,
+    int has_sink, float sink_log2, int* __restrict__ err) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int pitch_k = dk + 8, pitch_v = dv + 8;
+  // two stages of (K tile, V tile); the first K tile's place holds the Q tile to begin with
+  const size_t stage_elems = (size_t)PWM_KEYS * (pitch_k + pitch_v);
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+
+  const int b = blockIdx.z, g = blockIdx.y;
+  const int Gh = nh / nkv;
+  const int t0 = q_start[b], n_tok = q_start[b + 1] - t0;
+  const int rows_total = n_tok * Gh;
+  const int row0 = blockIdx.x * PWM_ROWS;
+  if (row0 >= rows_total) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* table = tables + (size_t)b * table_stride;
+  const int* s_table = s_tables ? s_tables + (size_t)b * s_table_stride : nullptr;
+
+  // the Q tile: row r is (token t0 + r / Gh, head g Gh + r % Gh)
+  {
+    const int chunks = dk >> 3;
+    for (int i = threadIdx.x; i < PWM_ROWS * chunks; i += PWM_THREADS) {
+      const int r = i / chunks, c = (i - r * chunks) << 3;
+      const int row = row0 + r;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < rows_total) {
+        const int tok = t0 + row / Gh, head = g * Gh + row % Gh;
+        v = *reinterpret_cast<const uint4*>(q + ((size_t)tok * nh + head) * dk + c);
+      }
+      *reinterpret_cast<uint4*>(Ks + (size_t)r * pitch_k + c) = v;
+    }
+  }
+  __syncthreads();
+  uint32_t qf[DKS][4];
+#pragma unroll
+  for (int ks = 0; ks < DKS; ++ks)
+    if (ks * 16 < dk)
+      pwm_ldmatrix_x4(qf[ks], Ks + (size_t)(warp * 16 + (lane & 15)) * pitch_k + ks * 16 +
+                                  (lane >> 4) * 8);
+  __syncthreads();
+
+  // this thread's two rows and their positions (-1: no such row)
+  const int p_first = positions[t0];
+  int my_p[2], my_j0[2], my_nb[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + warp * 16 + (lane >> 2) + 8 * i;
+    const int p = row < rows_total ? p_first + row / Gh : -1;
+    my_p[i] = p;
+    my_j0[i] = window > 0 ? max(0, p - window + 1) : 0;
+    my_nb[i] = (window > 0 && pool > 0 && p - window + 1 > 0) ? (p - window + 1) / pool : 0;
+  }
+  const int last_row = min(rows_total, row0 + PWM_ROWS) - 1;
+  const int p_lo = p_first + row0 / Gh, p_hi = p_first + last_row / Gh;
+  const int nb_hi = (window > 0 && pool > 0 && s_table && p_hi - window + 1 > 0)
+                        ? (p_hi - window + 1) / pool : 0;
+  const int block_tiles = (nb_hi + PWM_KEYS - 1) / PWM_KEYS;
+  const int j_lo = window > 0 ? max(0, p_lo - window + 1) : 0;     // the first key any row sees
+  const int first_tile = j_lo / PWM_KEYS;
+  const int token_tiles = p_hi / PWM_KEYS - first_tile + 1;
+
+  float m[2] = {-1e30f, -1e30f}, l[2] = {0.f, 0.f};
+  float o[DVT][4];
+#pragma unroll
+  for (int n = 0; n < DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  const int n_tiles = block_tiles + token_tiles;
+  const PwmPieces pk = pwm_pieces(dk), pv = pwm_pieces(dv);
+  const int ps_shift = (page_size & (page_size - 1)) ? -1 : 31 - __clz(page_size);
+  const int sps_shift = (s_page_size & (s_page_size - 1)) ? -1 : 31 - __clz(s_page_size);
+  auto issue = [&](int it) {                      // tile `it` on its way into stage it % 2
+    __nv_bfloat16* kt = Ks + (size_t)(it & 1) * stage_elems;
+    __nv_bfloat16* vt = kt + (size_t)PWM_KEYS * pitch_k;
+    if (it < block_tiles) {
+      const int base = it * PWM_KEYS;
+      pwm_load_tile(kt, pitch_k, pk, ks_cache, s_table, base, 0, nb_hi, dk, nkv, g, s_page_size,
+                    sps_shift, s_num_pages, err);
+      pwm_load_tile(vt, pitch_v, pv, vs_cache, s_table, base, 0, nb_hi, dv, nkv, g, s_page_size,
+                    sps_shift, s_num_pages, err);
+    } else {
+      const int base = (first_tile + it - block_tiles) * PWM_KEYS;
+      pwm_load_tile(kt, pitch_k, pk, k_cache, table, base, j_lo, p_hi + 1, dk, nkv, g, page_size,
+                    ps_shift, num_pages, err);
+      pwm_load_tile(vt, pitch_v, pv, v_cache, table, base, j_lo, p_hi + 1, dv, nkv, g, page_size,
+                    ps_shift, num_pages, err);
+    }
+  };
+  issue(0);
+  pwm_commit();
+  for (int it = 0; it < n_tiles; ++it) {
+    const bool blocks = it < block_tiles;
+    const int base = blocks ? it * PWM_KEYS : (first_tile + it - block_tiles) * PWM_KEYS;
+    if (it + 1 < n_tiles) issue(it + 1);          // the next tile travels while this one is used
+    pwm_commit();
+    pwm_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* Kt = Ks + (size_t)(it & 1) * stage_elems;
+    const __nv_bfloat16* Vs = Kt + (size_t)PWM_KEYS * pitch_k;
+
+    float s[PWM_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < PWM_KEYS / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < DKS; ++ks) {
+      if (ks * 16 < dk) {
+#pragma unroll
+        for (int np = 0; np < PWM_KEYS / 16; ++np) {
+          uint32_t kb[4];
+          pwm_ldmatrix_x4(kb, Kt + (size_t)(np * 16 + (lane & 7) + ((lane >> 4) << 3)) * pitch_k +
+                                  ks * 16 + ((lane >> 3) & 1) * 8);
+          pwm_mma(s[2 * np], qf[ks], kb[0], kb[1]);
+          pwm_mma(s[2 * np + 1], qf[ks], kb[2], kb[3]);
+        }
+      }
+    }
+    // mask by each row's own position, scale, running maximum
+    float mx[2] = {-1e30f, -1e30f};
+    unsigned valid[2] = {0u, 0u};                 // bit n*2+e: column n*8 + 2*(lane%4) + e
+#pragma unroll
+    for (int n = 0; n < PWM_KEYS / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int kj = base + n * 8 + 2 * (lane & 3) + (e & 1);
+        const bool ok = blocks ? kj < my_nb[i] : (kj >= my_j0[i] && kj <= my_p[i]);
+        s[n][e] *= scale_log2;
+        if (ok) {
+          valid[i] |= 1u << (n * 2 + (e & 1));
+          mx[i] = fmaxf(mx[i], s[n][e]);
+        }
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float m_new = fmaxf(m[i], mx[i]);
+      corr[i] = exp2f(m[i] - m_new);
+      m[i] = m_new;
+      l[i] *= corr[i];
+    }
+#pragma unroll
+    for (int n = 0; n < DVT; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int n = 0; n < PWM_KEYS / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const float pv = (valid[i] >> (n * 2 + (e & 1))) & 1u ? exp2f(s[n][e] - m[i]) : 0.f;
+        s[n][e] = pv;
+        l[i] += pv;
+      }
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < PWM_KEYS / 16; ++kk) {
+      uint32_t pa[4];
+      pa[0] = pwm_pack(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pwm_pack(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pwm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pwm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < DVT / 2; ++np) {
+        if (np * 16 < dv) {
+          uint32_t vb[4];
+          pwm_ldmatrix_x4_trans(vb, Vs + (size_t)(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) *
+                                             pitch_v + np * 16 + (lane >> 4) * 8);
+          pwm_mma(o[2 * np], pa, vb[0], vb[1]);
+          pwm_mma(o[2 * np + 1], pa, vb[2], vb[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  pwm_wait<0>();
+  // the denominator (with the sink), the turn back, the gate, the store
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    if (has_sink) {
+      const float m_new = fmaxf(m[i], sink_log2);
+      const float c = exp2f(m[i] - m_new);
+      l[i] = l[i] * c + exp2f(sink_log2 - m_new);
+#pragma unroll
+      for (int n = 0; n < DVT; ++n) {
+        o[n][2 * i] *= c;
+        o[n][2 * i + 1] *= c;
+      }
+    }
+  }
+  // normalised rows to shared memory (the key and value tiles are done with) ...
+  float* Os = reinterpret_cast<float*>(smem_raw);                 // [64][dv]
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + (lane >> 2) + 8 * i;
+    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+#pragma unroll
+    for (int n = 0; n < DVT; ++n) {
+      if (n * 8 < dv)
+        *reinterpret_cast<float2*>(Os + (size_t)r * dv + n * 8 + 2 * (lane & 3)) =
+            make_float2(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+  }
+  __syncthreads();
+  // ... then pair by pair: turned back by the row's position, times the head's gate
+  const int half = dv >> 1;
+  for (int idx = threadIdx.x; idx < PWM_ROWS * half; idx += PWM_THREADS) {
+    const int r = idx / half, mi = idx - r * half;
+    const int row = row0 + r;
+    if (row >= rows_total) break;
+    const int tok = t0 + row / Gh, head = g * Gh + row % Gh;
+    const int iu = interleaved ? 2 * mi : mi, iv = interleaved ? 2 * mi + 1 : mi + half;
+    float u = Os[(size_t)r * dv + iu], v = Os[(size_t)r * dv + iv];
+    if (v_inv_freq) {
+      float sn, cs;
+      sincosf((float)(p_first + row / Gh) * v_inv_freq[mi], &sn, &cs);
+      const float a = u * cs + v * sn, c = v * cs - u * sn;
+      u = a;
+      v = c;
+    }
+    float gt = 1.f;
+    if (gate) gt = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)tok * gate_stride + head])));
+    __nv_bfloat16* dst = out + ((size_t)tok * nh + head) * dv;
+    dst[iu] = __float2bfloat16_rn(u * gt);
+    dst[iv] = __float2bfloat16_rn(v * gt);
+  }
+}
+
+// max_rows: the most rows (tokens x heads of a group) that one request brings to this step.
+BF_EXPORT int bf_pwm_attention(
+    const void* q, const void* k_cache, const void* v_cache, const void* ks_cache,
+    const void* vs_cache, const int* q_start, const int* positions, const int* tables,
+    int table_stride, const int* s_tables, int s_table_stride, const void* gate,
+    long long gate_stride, const float* v_inv_freq, int interleaved, void* out, int B,
+    int max_tokens, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
+    int s_page_size, int s_num_pages, int window, int pool, float scale, int has_sink,
+    float sink, int* err, cudaStream_t stream) {
+  if (B <= 0 || max_tokens <= 0) return 0;
+  if (dk % 16 || dv % 16 || dk > 128 || dv > 128 || nkv <= 0 || nh % nkv || nh / nkv > 64)
+    return (int)cudaErrorInvalidValue;
+  if (pool > 0 && window > 0 && !ks_cache) return (int)cudaErrorInvalidValue;
+  const int Gh = nh / nkv;
+  dim3 grid((max_tokens * Gh + PWM_ROWS - 1) / PWM_ROWS, nkv, B);
+  size_t smem = 2 * (size_t)PWM_KEYS * ((dk + 8) + (dv + 8)) * sizeof(__nv_bfloat16);
+  if (smem < (size_t)PWM_ROWS * dv * sizeof(float)) smem = (size_t)PWM_ROWS * dv * sizeof(float);
+  const float log2e = 1.4426950408889634f;
+  auto kern = pwm_attention_kernel<8, 16>;
+  static bool configured[BF_MAX_DEVICES];
+  const int dev = bf_current_device();
+  if (!configured[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               2 * PWM_KEYS * (136 + 136) * 2);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = true;
+  }
+  kern<<<grid, PWM_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+      (const __nv_bfloat16*)ks_cache, (const __nv_bfloat16*)vs_cache, q_start, positions, tables,
+      table_stride, s_tables, s_table_stride, (const __nv_bfloat16*)gate, gate_stride, v_inv_freq,
+      interleaved, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, s_page_size,
+      s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, err);
+  return bf_launch_status();
+}

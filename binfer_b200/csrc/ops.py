@@ -543,6 +543,41 @@ def apw_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
          _ptr(err), _stream())
 
 
+def pwm_attention_takes(dtype: torch.dtype, nh: int, nkv: int, dk: int, dv: int) -> bool:
+    """Whether the tensor-core kernel of the pooled-window attention takes these sizes."""
+    return (dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and dk <= 128
+            and dv <= 128 and nh // nkv <= 64)
+
+
+def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  ks_cache: Optional[torch.Tensor], vs_cache: Optional[torch.Tensor],
+                  q_start: torch.Tensor, positions: torch.Tensor, tables: torch.Tensor,
+                  s_tables: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                  v_inv_freq: Optional[torch.Tensor], interleaved: bool, out: torch.Tensor,
+                  B: int, max_tokens: int, nh: int, nkv: int, dk: int, dv: int,
+                  window: Optional[int], pool: int, scale: float, sink: Optional[float],
+                  err: torch.Tensor) -> None:
+    """``apw_attention`` on the tensor cores (bfloat16; sizes: ``pwm_attention_takes``):
+    request ``b`` of the batch owns the token rows ``q_start[b] .. q_start[b+1]-1``, at most
+    ``max_tokens`` of them."""
+    if not pwm_attention_takes(q.dtype, nh, nkv, dk, dv):
+        raise KernelError("pwm_attention: bfloat16, head sizes multiples of 16 up to 128")
+    if not q.is_contiguous() or not out.is_contiguous() or q.data_ptr() % 16:
+        raise KernelError("pwm_attention: q and out must be contiguous and 16-byte aligned")
+    if gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise KernelError("pwm_attention: gate rows must be contiguous and of q's type")
+    has_s = ks_cache is not None
+    _run("pwm_attention", lib().bf_pwm_attention, _ptr(q), _ptr(k_cache), _ptr(v_cache),
+         _ptr(ks_cache), _ptr(vs_cache), _ptr(q_start), _ptr(positions), _ptr(tables),
+         _c_int(tables.stride(0)), _ptr(s_tables), _c_int(s_tables.stride(0) if has_s else 0),
+         _ptr(gate), _c_ll(gate.stride(0) if gate is not None else 0), _ptr(v_inv_freq),
+         _c_int(1 if interleaved else 0), _ptr(out), _c_int(B), _c_int(max_tokens), _c_int(nh),
+         _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
+         _c_int(ks_cache.shape[2] if has_s else 1), _c_int(ks_cache.shape[0] if has_s else 0),
+         _c_int(window or 0), _c_int(pool if has_s else 0), _c_float(scale),
+         _c_int(0 if sink is None else 1), _c_float(sink or 0.0), _ptr(err), _stream())
+
+
 # ------------------------------------------------------------- matrix products
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic."""

@@ -15,6 +15,7 @@ be cut anywhere and portions can share a step with decoded tokens.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -25,6 +26,11 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import BuildEnv, EntryView, Mixer, StepContext, build_position, register_mixer
 from .linear import linear
+
+
+# BINFER_B200_PWA_TENSOR_CORES=0: the one-warp-per-row kernel also in bfloat16 (the float32
+# engine always runs it: its sums have one fixed order per position)
+TENSOR_CORES = os.environ.get("BINFER_B200_PWA_TENSOR_CORES", "1") != "0"
 
 
 class PooledWindowAttention(Mixer):
@@ -117,6 +123,15 @@ class PooledWindowAttention(Mixer):
             s_tables = ctx.block_tables[sg]
         gate = proj[:, self.gate_off:self.gate_off + self.H] if s.head_gate else None
         out = torch.empty((T, self.H * self.dv), dtype=x.dtype, device=x.device)
+        if TENSOR_CORES and ops.pwm_attention_takes(x.dtype, self.H, self.G, self.dk, self.dv):
+            # bfloat16: tiles of (token, head of a group) rows on the tensor cores, prompt
+            # portions and single tokens alike
+            ops.pwm_attention(q, view.k_cache, view.v_cache, ks, vs, ctx.q_start, ctx.positions,
+                              ctx.block_tables[g], s_tables, gate, v_inv, s.interleaved, out,
+                              ctx.B, 1 if ctx.decode_only else ctx.max_q_len, self.H, self.G,
+                              self.dk, self.dv, s.window, self.pool, s.softmax_scale, s.sink,
+                              ctx.err)
+            return linear(out, self.w_o)
         ops.apw_attention(q, view.k_cache, view.v_cache, ks, vs, ctx.seq_of_token, ctx.positions,
                           ctx.block_tables[g], s_tables, gate, v_inv, s.interleaved, out, self.H,
                           self.G, self.dk, self.dv, s.window, self.pool, s.softmax_scale, s.sink,

@@ -76,7 +76,8 @@ def _one_layer(layer, vocab=260, width=48, scale=4.0, eps=1e-6):
 
 
 @pytest.mark.parametrize("heads,dk,dv,cap,ff", [(2, 16, 32, 8.0, None), (1, 40, 24, 2.0, 64),
-                                                (3, 8, 8, 30.0, None), (2, 72, 96, 6.0, None)])
+                                                (3, 8, 8, 30.0, None), (2, 72, 96, 6.0, None),
+                                                (2, 12, 20, 9.0, None), (1, 256, 40, 12.0, None)])
 def test_matrix_memory_alone(cuda_device, tmp_path, heads, dk, dv, cap, ff):
     """One memory layer: a prompt at once, portions, and token by token from the first
     token on, over 200 tokens.  The gate weights are scaled up so that pre-activations
@@ -111,8 +112,8 @@ def _stand_out(raw, toks, marked, layer=0, amp=2.0, boost=20.0):
         p = f"l{layer}.mix."
         gen = torch.Generator().manual_seed(9)
         e = torch.randn(w["embed"].shape[1], generator=gen)
-        e = e / e.norm()
-        a = torch.randn(dk, generator=gen)
+        e = (e / e.norm()).to(w["embed"].dtype)
+        a = torch.randn(dk, generator=gen).to(w["embed"].dtype)
         w["embed"] -= torch.outer(w["embed"] @ e, e)
         for pos in marked:
             w["embed"][toks[pos]] += e * amp / raw["embedding"]["scale"]
@@ -178,6 +179,51 @@ def test_attention_sink_and_first_tokens(cuda_device, tmp_path):
     ref = {"a": G.forward(raw, w, toks)}
     steps = H.trace_decode_tail({"a": toks}, tail=8)
     _compare(H.run_trace(_runner(d, torch.float32, 16, 2), steps), ref, torch.float32, "sink")
+
+
+def test_tensor_core_attention_beside_the_plain_kernel(cuda_device, tmp_path):
+    """bfloat16: the tiled tensor-core kernel (rows of a group's heads side by side, prompt
+    portions and single tokens) and the one-warp-per-row kernel give the same logits to
+    rounding, on a case whose marked keys make a wrong mask show."""
+    import importlib
+    from binfer_b200.csrc import ops
+    mod = importlib.import_module("binfer_b200.parts.attention_pooled")
+    W, P, T = 40, 8, 300
+    mx = H._guk_attn(6, 2, 32, 48, W, P, 16, scale=0.4)
+    raw = _one_layer(H._guk_layer("attention", mx, 64), vocab=500, width=64)
+    toks = _distinct_tokens(T, 500, 33)
+    marked = list(range(16, 24)) + [100, 139, 140, 250, 299]
+    d = H.make_gukidra_dir(tmp_path, "A", torch.bfloat16, raw=raw,
+                           tweak=_stand_out(raw, toks, marked), tag="tc")
+    raw, w = H.read_model_dir(d)
+    ref = {"a": G.forward(raw, w, toks)}
+    outs = []
+    for on in (True, False):
+        seen = set()
+
+        class Names:
+            def begin(self, name):
+                seen.add(name)
+
+            def end(self, name):
+                pass
+
+        mod.TENSOR_CORES = on
+        ops.set_profiler(Names())
+        try:
+            got = {}
+            for name, steps in _all_regimes({"a": toks}, tail=70).items():
+                got[name] = H.run_trace(_runner(d, torch.bfloat16, 16, H.peak_pages(steps, 16)),
+                                        steps)
+                _compare(got[name], ref, torch.bfloat16, f"tensor cores {on}/{name}")
+        finally:
+            ops.set_profiler(None)
+            mod.TENSOR_CORES = True
+        assert ("pwm_attention" in seen) == on and ("apw_attention" in seen) != on
+        outs.append(got)
+    for name in outs[0]:
+        worst = max(H.rel_err(outs[0][name][k], outs[1][name][k]) for k in outs[0][name])
+        assert worst <= 0.05, f"{name}: the two kernels differ by {worst:.3g}"
 
 
 # ----------------------------------------------------------------------- whole models
