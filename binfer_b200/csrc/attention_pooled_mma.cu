@@ -41,6 +41,11 @@ __device__ __forceinline__ void pwm_mma(float (&c)[4], const uint32_t (&a)[4], u
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float pwm_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pwm_pack(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -79,7 +84,9 @@ __device__ __forceinline__ PwmPieces pwm_pieces(int d) {
 // before `lo` or at or beyond `limit` are zeroed (their pages may be gone).  The pages of a
 // thread's pieces are looked up first, all at once, so that the lookups' round trips overlap.
 // `ps_shift`: log2 of the page size, or -1 if that is no power of two.
-__device__ __forceinline__ void pwm_load_tile(__nv_bfloat16* tile, int pitch, const PwmPieces& pc,
+// (Not inlined: the tile loop's code must stay small enough for the instruction cache, which
+// a single resident warp per scheduler cannot hide misses of.)
+__device__ __noinline__ void pwm_load_tile(__nv_bfloat16* tile, int pitch, const PwmPieces& pc,
                                               const __nv_bfloat16* __restrict__ cache,
                                               const int* __restrict__ table, int first, int lo,
                                               int limit, int d, int nkv, int g, int page_size,
@@ -108,7 +115,10 @@ __device__ __forceinline__ void pwm_load_tile(__nv_bfloat16* tile, int pitch, co
   }
 }
 
-template <int DKS, int DVT>          // key size <= 16 DKS, value size <= 8 DVT
+// SPLIT: at most 16 rows (a single token's heads of a group, while decoding).  All four warps
+// then take the same rows and every fourth key tile each, four tiles in flight at a time,
+// and their partial results (maximum, sum, unnormalised output) are merged at the end.
+template <int DKS, int DVT, bool SPLIT>   // key size <= 16 DKS, value size <= 8 DVT
 __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ ks_cache,
@@ -132,6 +142,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   const int row0 = blockIdx.x * PWM_ROWS;
   if (row0 >= rows_total) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wrow = SPLIT ? 0 : warp * 16;          // the warp's first row inside the tile
   const int* table = tables + (size_t)b * table_stride;
   const int* s_table = s_tables ? s_tables + (size_t)b * s_table_stride : nullptr;
 
@@ -154,7 +165,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
 #pragma unroll
   for (int ks = 0; ks < DKS; ++ks)
     if (ks * 16 < dk)
-      pwm_ldmatrix_x4(qf[ks], Ks + (size_t)(warp * 16 + (lane & 15)) * pitch_k + ks * 16 +
+      pwm_ldmatrix_x4(qf[ks], Ks + (size_t)(wrow + (lane & 15)) * pitch_k + ks * 16 +
                                   (lane >> 4) * 8);
   __syncthreads();
 
@@ -163,7 +174,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   int my_p[2], my_j0[2], my_nb[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int row = row0 + warp * 16 + (lane >> 2) + 8 * i;
+    const int row = row0 + wrow + (lane >> 2) + 8 * i;
     const int p = row < rows_total ? p_first + row / Gh : -1;
     my_p[i] = p;
     my_j0[i] = window > 0 ? max(0, p - window + 1) : 0;
@@ -187,33 +198,46 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   const PwmPieces pk = pwm_pieces(dk), pv = pwm_pieces(dv);
   const int ps_shift = (page_size & (page_size - 1)) ? -1 : 31 - __clz(page_size);
   const int sps_shift = (s_page_size & (s_page_size - 1)) ? -1 : 31 - __clz(s_page_size);
-  auto issue = [&](int it) {                      // tile `it` on its way into stage it % 2
-    __nv_bfloat16* kt = Ks + (size_t)(it & 1) * stage_elems;
+  auto issue = [&](int it, int stage) {           // tile `it` on its way into a stage
+    __nv_bfloat16* kt = Ks + (size_t)stage * stage_elems;
     __nv_bfloat16* vt = kt + (size_t)PWM_KEYS * pitch_k;
-    if (it < block_tiles) {
-      const int base = it * PWM_KEYS;
-      pwm_load_tile(kt, pitch_k, pk, ks_cache, s_table, base, 0, nb_hi, dk, nkv, g, s_page_size,
-                    sps_shift, s_num_pages, err);
-      pwm_load_tile(vt, pitch_v, pv, vs_cache, s_table, base, 0, nb_hi, dv, nkv, g, s_page_size,
-                    sps_shift, s_num_pages, err);
-    } else {
-      const int base = (first_tile + it - block_tiles) * PWM_KEYS;
-      pwm_load_tile(kt, pitch_k, pk, k_cache, table, base, j_lo, p_hi + 1, dk, nkv, g, page_size,
-                    ps_shift, num_pages, err);
-      pwm_load_tile(vt, pitch_v, pv, v_cache, table, base, j_lo, p_hi + 1, dv, nkv, g, page_size,
-                    ps_shift, num_pages, err);
-    }
+    const bool bl = it < block_tiles;
+    const int base = bl ? it * PWM_KEYS : (first_tile + it - block_tiles) * PWM_KEYS;
+    const int* tb = bl ? s_table : table;
+    const int lo = bl ? 0 : j_lo, limit = bl ? nb_hi : p_hi + 1;
+    const int ps = bl ? s_page_size : page_size, sh = bl ? sps_shift : ps_shift;
+    const int np = bl ? s_num_pages : num_pages;
+    pwm_load_tile(kt, pitch_k, pk, bl ? ks_cache : k_cache, tb, base, lo, limit, dk, nkv, g, ps,
+                  sh, np, err);
+    pwm_load_tile(vt, pitch_v, pv, bl ? vs_cache : v_cache, tb, base, lo, limit, dv, nkv, g, ps,
+                  sh, np, err);
   };
-  issue(0);
-  pwm_commit();
-  for (int it = 0; it < n_tiles; ++it) {
+  if (!SPLIT) {
+    issue(0, 0);
+    pwm_commit();
+  }
+  for (int g0 = 0; g0 < n_tiles; g0 += SPLIT ? 4 : 1) {
+    int it, stage;
+    if (SPLIT) {                                  // four tiles at a time, one a warp
+#pragma unroll 1
+      for (int x = 0; x < 4; ++x)
+        if (g0 + x < n_tiles) issue(g0 + x, x);
+      pwm_commit();
+      pwm_wait<0>();
+      it = g0 + warp;
+      stage = warp;
+    } else {
+      if (g0 + 1 < n_tiles) issue(g0 + 1, (g0 + 1) & 1);   // travels while this one is used
+      pwm_commit();
+      pwm_wait<1>();
+      it = g0;
+      stage = g0 & 1;
+    }
+    __syncthreads();
+    if (it < n_tiles) {
     const bool blocks = it < block_tiles;
     const int base = blocks ? it * PWM_KEYS : (first_tile + it - block_tiles) * PWM_KEYS;
-    if (it + 1 < n_tiles) issue(it + 1);          // the next tile travels while this one is used
-    pwm_commit();
-    pwm_wait<1>();
-    __syncthreads();
-    const __nv_bfloat16* Kt = Ks + (size_t)(it & 1) * stage_elems;
+    const __nv_bfloat16* Kt = Ks + (size_t)stage * stage_elems;
     const __nv_bfloat16* Vs = Kt + (size_t)PWM_KEYS * pitch_k;
 
     float s[PWM_KEYS / 8][4];
@@ -232,31 +256,52 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
         }
       }
     }
-    // mask by each row's own position, scale, running maximum
+    // Each row masks by its own position; a tile that every row of this warp sees whole (the
+    // common case inside a window) skips the tests.  Scores stay unscaled: the scale rides on
+    // the exponent's multiply-add.
+    const int w_first = min(row0 + wrow, rows_total - 1), w_last = min(row0 + wrow + 15,
+                                                                       rows_total - 1);
+    const int wp_lo = p_first + w_first / Gh, wp_hi = p_first + w_last / Gh;
+    const bool whole_rows = row0 + wrow + 15 < rows_total;
+    const bool whole_tile =
+        whole_rows && (blocks ? base + PWM_KEYS <= ((window > 0 && pool > 0 && wp_lo - window + 1 > 0)
+                                                        ? (wp_lo - window + 1) / pool : 0)
+                              : (base >= (window > 0 ? max(0, wp_hi - window + 1) : 0) &&
+                                 base + PWM_KEYS - 1 <= wp_lo));
     float mx[2] = {-1e30f, -1e30f};
-    unsigned valid[2] = {0u, 0u};                 // bit n*2+e: column n*8 + 2*(lane%4) + e
+    unsigned valid[2] = {0xffffu, 0xffffu};       // bit n*2+e: column n*8 + 2*(lane%4) + e
+    if (whole_tile) {
 #pragma unroll
-    for (int n = 0; n < PWM_KEYS / 8; ++n) {
+      for (int n = 0; n < PWM_KEYS / 8; ++n) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+      }
+    } else {
+      valid[0] = valid[1] = 0u;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int kj = base + n * 8 + 2 * (lane & 3) + (e & 1);
-        const bool ok = blocks ? kj < my_nb[i] : (kj >= my_j0[i] && kj <= my_p[i]);
-        s[n][e] *= scale_log2;
-        if (ok) {
-          valid[i] |= 1u << (n * 2 + (e & 1));
-          mx[i] = fmaxf(mx[i], s[n][e]);
+      for (int n = 0; n < PWM_KEYS / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int kj = base + n * 8 + 2 * (lane & 3) + (e & 1);
+          const bool ok = blocks ? kj < my_nb[i] : (kj >= my_j0[i] && kj <= my_p[i]);
+          if (ok) {
+            valid[i] |= 1u << (n * 2 + (e & 1));
+            mx[i] = fmaxf(mx[i], s[n][e]);
+          }
         }
       }
     }
-    float corr[2];
+    float corr[2], m_scaled[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      const float m_new = fmaxf(m[i], mx[i]);
-      corr[i] = exp2f(m[i] - m_new);
+      // m holds the running maximum of the scaled scores (the scale is positive)
+      const float m_new = fmaxf(m[i], mx[i] > -1e29f ? mx[i] * scale_log2 : -1e30f);
+      corr[i] = pwm_ex2(m[i] - m_new);
       m[i] = m_new;
+      m_scaled[i] = -m_new;
       l[i] *= corr[i];
     }
 #pragma unroll
@@ -269,7 +314,8 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = e >> 1;
-        const float pv = (valid[i] >> (n * 2 + (e & 1))) & 1u ? exp2f(s[n][e] - m[i]) : 0.f;
+        float pv = pwm_ex2(fmaf(s[n][e], scale_log2, m_scaled[i]));
+        if (!whole_tile && !((valid[i] >> (n * 2 + (e & 1))) & 1u)) pv = 0.f;
         s[n][e] = pv;
         l[i] += pv;
       }
@@ -293,15 +339,71 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
         }
       }
     }
+    }
     __syncthreads();
   }
 
   pwm_wait<0>();
-  // the denominator (with the sink), the turn back, the gate, the store
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  if (SPLIT) {
+    // the four warps' partial results of the same 16 rows become one: through shared memory
+    // (the tiles are done with), every warp then holds the merged rows
+    float* Ow = reinterpret_cast<float*>(smem_raw);               // [4][16][dv]
+    float* Mw = Ow + 4 * 16 * dv;                                 // [4][16]
+    float* Lw = Mw + 4 * 16;                                      // [4][16]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = (lane >> 2) + 8 * i;
+      if ((lane & 3) == 0) {
+        Mw[warp * 16 + r] = m[i];
+        Lw[warp * 16 + r] = l[i];
+      }
+#pragma unroll
+      for (int n = 0; n < DVT; ++n)
+        if (n * 8 < dv)
+          *reinterpret_cast<float2*>(Ow + ((size_t)warp * 16 + r) * dv + n * 8 + 2 * (lane & 3)) =
+              make_float2(o[n][2 * i], o[n][2 * i + 1]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = (lane >> 2) + 8 * i;
+      float mm = -1e30f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mw[w * 16 + r]);
+      float f[4], ll = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        f[w] = pwm_ex2(Mw[w * 16 + r] - mm);
+        ll += Lw[w * 16 + r] * f[w];
+      }
+      m[i] = mm;
+      l[i] = ll;
+#pragma unroll
+      for (int n = 0; n < DVT; ++n) {
+        if (n * 8 < dv) {
+          float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float2 x = *reinterpret_cast<const float2*>(
+                Ow + ((size_t)w * 16 + r) * dv + n * 8 + 2 * (lane & 3));
+            acc.x += x.x * f[w];
+            acc.y += x.y * f[w];
+          }
+          o[n][2 * i] = acc.x;
+          o[n][2 * i + 1] = acc.y;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // the denominator (with the sink), the turn back, the gate, the store
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
     if (has_sink) {
       const float m_new = fmaxf(m[i], sink_log2);
       const float c = exp2f(m[i] - m_new);
@@ -317,7 +419,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   float* Os = reinterpret_cast<float*>(smem_raw);                 // [64][dv]
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int r = warp * 16 + (lane >> 2) + 8 * i;
+    const int r = wrow + (lane >> 2) + 8 * i;     // (SPLIT: every warp writes the same values)
     const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
 #pragma unroll
     for (int n = 0; n < DVT; ++n) {
@@ -364,19 +466,22 @@ BF_EXPORT int bf_pwm_attention(
   if (dk % 16 || dv % 16 || dk > 128 || dv > 128 || nkv <= 0 || nh % nkv || nh / nkv > 64)
     return (int)cudaErrorInvalidValue;
   if (pool > 0 && window > 0 && !ks_cache) return (int)cudaErrorInvalidValue;
+  if (!(scale > 0.f)) return (int)cudaErrorInvalidValue;     // the running maximum relies on it
   const int Gh = nh / nkv;
   dim3 grid((max_tokens * Gh + PWM_ROWS - 1) / PWM_ROWS, nkv, B);
-  size_t smem = 2 * (size_t)PWM_KEYS * ((dk + 8) + (dv + 8)) * sizeof(__nv_bfloat16);
-  if (smem < (size_t)PWM_ROWS * dv * sizeof(float)) smem = (size_t)PWM_ROWS * dv * sizeof(float);
+  const bool split = max_tokens * Gh <= 16;       // single tokens: the keys shared out over warps
+  size_t smem = (split ? 4 : 2) * (size_t)PWM_KEYS * ((dk + 8) + (dv + 8)) * sizeof(__nv_bfloat16);
+  if (smem < (size_t)PWM_ROWS * dv * sizeof(float) + 512)
+    smem = (size_t)PWM_ROWS * dv * sizeof(float) + 512;
   const float log2e = 1.4426950408889634f;
-  auto kern = pwm_attention_kernel<8, 16>;
-  static bool configured[BF_MAX_DEVICES];
+  auto kern = split ? pwm_attention_kernel<8, 16, true> : pwm_attention_kernel<8, 16, false>;
+  static bool configured[BF_MAX_DEVICES][2];
   const int dev = bf_current_device();
-  if (!configured[dev]) {
+  if (!configured[dev][split]) {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               2 * PWM_KEYS * (136 + 136) * 2);
+                                               (split ? 4 : 2) * PWM_KEYS * (136 + 136) * 2);
     if (e != cudaSuccess) return (int)e;
-    configured[dev] = true;
+    configured[dev][split] = true;
   }
   kern<<<grid, PWM_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,

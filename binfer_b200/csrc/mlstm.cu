@@ -335,6 +335,7 @@ __global__ void __launch_bounds__(128) mlstm_scan2_kernel(
     }
     const float4* k4 = reinterpret_cast<const float4*>(ks + lane * (R + PAD));
     const float4* q4 = reinterpret_cast<const float4*>(qs + lane * (R + PAD));
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
       const float a = __shfl_sync(0xffffffffu, my_a, tt);
       const float bb = __shfl_sync(0xffffffffu, my_b, tt);

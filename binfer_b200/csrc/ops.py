@@ -546,7 +546,7 @@ def apw_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 def pwm_attention_takes(dtype: torch.dtype, nh: int, nkv: int, dk: int, dv: int) -> bool:
     """Whether the tensor-core kernel of the pooled-window attention takes these sizes."""
     return (dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and dk <= 128
-            and dv <= 128 and nh // nkv <= 64)
+            and dv <= 128 and nh // nkv <= 64)      # (and a positive score scale)
 
 
 def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -123,7 +123,8 @@ class PooledWindowAttention(Mixer):
             s_tables = ctx.block_tables[sg]
         gate = proj[:, self.gate_off:self.gate_off + self.H] if s.head_gate else None
         out = torch.empty((T, self.H * self.dv), dtype=x.dtype, device=x.device)
-        if TENSOR_CORES and ops.pwm_attention_takes(x.dtype, self.H, self.G, self.dk, self.dv):
+        if (TENSOR_CORES and s.softmax_scale > 0
+                and ops.pwm_attention_takes(x.dtype, self.H, self.G, self.dk, self.dv)):
             # bfloat16: tiles of (token, head of a group) rows on the tensor cores, prompt
             # portions and single tokens alike
             ops.pwm_attention(q, view.k_cache, view.v_cache, ks, vs, ctx.q_start, ctx.positions,
