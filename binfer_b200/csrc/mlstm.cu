@@ -20,7 +20,9 @@
 // ----------------------------------------------------------------------------- gates
 // gates[t, r] for r < heads:  cap tanh((w_r . h_t + b_r) / cap)          (log input gate)
 //             for r >= heads: logsigmoid(cap tanh((w_r . h_t + b_r) / cap))  (log forget gate)
-// One warp per (token, gate row); cap <= 0 means no cap.
+// One warp per (token, gate row); cap <= 0 means no cap.  (A warp that takes eight rows of a
+// token, so as to read the token's input once, measured five times slower at 2,048 tokens and
+// sixteen times slower at 8: too few warps, each a long chain.)
 template <typename A>
 __global__ void mlstm_gates_kernel(const A* __restrict__ h, long long h_stride,
                                    const A* __restrict__ w, const float* __restrict__ bias,
@@ -245,6 +247,7 @@ __global__ void __launch_bounds__(128) mlstm_scan2_kernel(
   // this thread's (at most four) 8-element pieces of a chunk's q and k: where each comes
   // from and where its two halves go, worked out once
   int it_tok[4], it_src[4], it_dst[4], it_dst2[4];
+  bool it_k[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int i = threadIdx.x + 128 * k;
@@ -252,10 +255,9 @@ __global__ void __launch_bounds__(128) mlstm_scan2_kernel(
     const int which = rest / dk8, r = (rest - which * dk8) * 8;
     it_tok[k] = i < items ? tok : MLSTM2_CH;       // MLSTM2_CH: no such piece
     it_src[k] = which * H * dk + head * dk + r;
-    // (k pieces are marked by an offset of a whole q array)
-    const int at = which * MLSTM2_CH * PITCH + tok * PITCH;
-    it_dst[k] = at + (r / R) * (R + PAD) + r % R;
-    it_dst2[k] = at + ((r + 4) / R) * (R + PAD) + (r + 4) % R;
+    it_k[k] = which != 0;
+    it_dst[k] = tok * PITCH + (r / R) * (R + PAD) + r % R;
+    it_dst2[k] = tok * PITCH + ((r + 4) / R) * (R + PAD) + (r + 4) % R;
   }
   using Raw = typename std::conditional<sizeof(A) == 2, uint4, float4>::type;
   constexpr int RAWS = sizeof(A) == 2 ? 1 : 2;
@@ -286,9 +288,8 @@ __global__ void __launch_bounds__(128) mlstm_scan2_kernel(
       if (it_tok[k] < n) {
         float x[8];
         mlstm_unpack8(raw[k], x);
-        const bool is_k = it_dst[k] >= MLSTM2_CH * PITCH;
-        const float f = is_k ? 1.f : q_scale;
-        float* dst = is_k ? ks - MLSTM2_CH * PITCH : qs;
+        const float f = it_k[k] ? 1.f : q_scale;
+        float* dst = it_k[k] ? ks : qs;
         *reinterpret_cast<float4*>(dst + it_dst[k]) =
             make_float4(x[0] * f, x[1] * f, x[2] * f, x[3] * f);
         *reinterpret_cast<float4*>(dst + it_dst2[k]) =
