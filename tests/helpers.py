@@ -343,7 +343,16 @@ GUK_D = {"architecture": "Gukidra", "vocab": 500, "width": 256, "norm": {"eps": 
                     _guk_layer("attention", _guk_attn(4, 1, 64, 128, 64, 16, 32, kv_from=1),
                                ff=384)]}
 
+# sizes that are multiples of two only: a width of 50, heads of 10 and 6, a vocabulary of 131
+GUK_E = {"architecture": "Gukidra", "vocab": 131, "width": 50, "norm": {"eps": 1e-6},
+         "embedding": {"scale": 2.5},
+         "layers": [_guk_layer("mlstm", _guk_mlstm(2, 6, 10, 7.0), ff=34),
+                    _guk_layer("attention", _guk_attn(2, 1, 10, 6, 9, 2, 6, base=3000.0), ff=46),
+                    _guk_layer("attention", _guk_attn(2, 1, 10, 6, 13, 3, 6, base=3000.0,
+                                                      kv_from=1))]}
+
 GUK = {
+    "E": dict(raw=GUK_E, std=0.12, norm_std=0.1, page_size=16, seed=9),
     "A": dict(raw=GUK_A, std=0.08, norm_std=0.1, page_size=16, seed=5),
     "B": dict(raw=GUK_B, std=0.1, norm_std=0.1, page_size=4, seed=6),
     "C": dict(raw=GUK_C, std=0.12, norm_std=0.1, page_size=8, seed=7),

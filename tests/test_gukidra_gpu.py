@@ -228,7 +228,7 @@ def test_tensor_core_attention_beside_the_plain_kernel(cuda_device, tmp_path):
 
 # ----------------------------------------------------------------------- whole models
 LENGTHS = {"A": [5, 17, 33, 70, 121], "B": [1, 9, 40, 70, 101], "C": [3, 30, 64, 47, 2],
-           "D": [2, 45, 150, 333, 90]}
+           "D": [2, 45, 150, 333, 90], "E": [4, 19, 37, 66, 83]}
 
 
 def _requests(which, extra=()):
@@ -255,9 +255,11 @@ def plain_logits(tmp_path_factory):
 
 
 @pytest.mark.parametrize("which,dtype", [("A", torch.float32), ("B", torch.float32),
-                                         ("C", torch.float32), ("A", torch.bfloat16),
-                                         ("B", torch.bfloat16), ("D", torch.bfloat16)],
-                         ids=["A-f32", "B-f32", "C-f32", "A-bf16", "B-bf16", "D-bf16"])
+                                         ("C", torch.float32), ("E", torch.float32),
+                                         ("A", torch.bfloat16), ("B", torch.bfloat16),
+                                         ("D", torch.bfloat16), ("E", torch.bfloat16)],
+                         ids=["A-f32", "B-f32", "C-f32", "E-f32", "A-bf16", "B-bf16", "D-bf16",
+                              "E-bf16"])
 @pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
 def test_replay(cuda_device, plain_logits, which, dtype, regime):
     """Seven requests through four state slots and page pools of exactly the peak need."""
@@ -314,8 +316,9 @@ def test_decoding_from_captured_steps(cuda_device, plain_logits):
 
 
 # ------------------------------------------------------------------------- generation
-@pytest.mark.parametrize("graphs,budget", [(True, 2048), (False, 7)], ids=["graphs", "portions"])
-def test_greedy_generation_through_the_engine(cuda_device, tmp_path, graphs, budget):
+@pytest.mark.parametrize("graphs,step_tokens", [(True, 2048), (False, 7)],
+                         ids=["graphs", "portions"])
+def test_greedy_generation_through_the_engine(cuda_device, tmp_path, graphs, step_tokens):
     """Prompts of 5/17/33/2 tokens through ``Engine.generate``: the scheduler's admission,
     portions of at most seven tokens beside decoding (second case), captured decode steps
     (first case); every token is the plain implementation's choice."""
@@ -324,7 +327,7 @@ def test_greedy_generation_through_the_engine(cuda_device, tmp_path, graphs, bud
     raw, w = H.read_model_dir(d)
     prompts = [H.random_tokens(n, raw["vocab"], n) for n in (5, 17, 33, 2)]
     eng = Engine(d, "float32", num_pages=40, page_size=16, max_seq_len=128, max_batch_size=3,
-                 max_tokens_per_step=budget, cuda_graphs=graphs)
+                 max_tokens_per_step=step_tokens, cuda_graphs=graphs)
     got = eng.generate(prompts, max_tokens=12, ignore_eos=True)
     for p, out in zip(prompts, got):
         assert len(out) == 12
@@ -337,3 +340,27 @@ def test_greedy_generation_through_the_engine(cuda_device, tmp_path, graphs, bud
     assert st["pages_free"] == st["pages_total"]
     if graphs:
         assert getattr(eng.runner, "graph_replays", 0) > 0
+
+
+def test_trace_replay_tool_with_four_state_slots(cuda_device, tmp_path):
+    """``bin/trace_run`` as a user runs it on a hybrid model: six requests through its four
+    state slots and a page pool sized by ``--max-tokens``."""
+    import test_trace_run_gpu as TR
+    d = H.make_gukidra_dir(tmp_path, "B")
+    raw, w = H.read_model_dir(d)
+    reqs = {f"r{i}": H.random_tokens(n, raw["vocab"], 31 * i + n)
+            for i, n in enumerate([70, 33, 90, 12, 64, 41])}
+    steps = H.trace_mixed(reqs)
+    live, peak = {}, 0
+    for st in steps:
+        for e in st["entries"]:
+            live[e["id"]] = live.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, sum(-(-n // 64) * 64 for n in live.values()))
+        for rid in st["end"]:
+            live.pop(rid)
+    out_dir = str(tmp_path / "out")
+    TR._replay(d, "float32", steps, out_dir, peak)
+    got = TR._collect(steps, out_dir, raw["vocab"])
+    ref = {rid: G.forward(raw, w, toks) for rid, toks in reqs.items()}
+    worst = max(H.rel_err(row, ref[rid][p]) for (rid, p), row in got.items())
+    assert got and worst <= TOL[torch.float32], f"worst relative error {worst:.3g}"
