@@ -128,7 +128,8 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     long long gate_stride, const float* __restrict__ v_inv_freq, int interleaved,
     __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
     int num_pages, int s_page_size, int s_num_pages, int window, int pool, float scale_log2,
-    int has_sink, float sink_log2, int* __restrict__ err) {
+    int has_sink, float sink_log2, float* __restrict__ part_o, float* __restrict__ part_ml,
+    int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch_k = dk + 8, pitch_v = dv + 8;
   // two stages of (K tile, V tile); the first K tile's place holds the Q tile to begin with
@@ -139,7 +140,10 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   const int Gh = nh / nkv;
   const int t0 = q_start[b], n_tok = q_start[b + 1] - t0;
   const int rows_total = n_tok * Gh;
-  const int row0 = blockIdx.x * PWM_ROWS;
+  // SPLIT with scratch for partial results: blockIdx.x is a share of the key tiles (four of
+  // them), not a tile of rows; pwm_merge_kernel makes the shares one
+  const bool shared_out = SPLIT && part_o != nullptr;
+  const int row0 = shared_out ? 0 : blockIdx.x * PWM_ROWS;
   if (row0 >= rows_total) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wrow = SPLIT ? 0 : warp * 16;          // the warp's first row inside the tile
@@ -195,6 +199,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   for (int n = 0; n < DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
   const int n_tiles = block_tiles + token_tiles;
+  if (shared_out && 4 * (int)blockIdx.x >= n_tiles) return;
   const PwmPieces pk = pwm_pieces(dk), pv = pwm_pieces(dv);
   const int ps_shift = (page_size & (page_size - 1)) ? -1 : 31 - __clz(page_size);
   const int sps_shift = (s_page_size & (s_page_size - 1)) ? -1 : 31 - __clz(s_page_size);
@@ -216,7 +221,9 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     issue(0, 0);
     pwm_commit();
   }
-  for (int g0 = 0; g0 < n_tiles; g0 += SPLIT ? 4 : 1) {
+  const int g_first = shared_out ? 4 * blockIdx.x : 0;
+  const int g_end = shared_out ? min(n_tiles, g_first + 4) : n_tiles;
+  for (int g0 = g_first; g0 < g_end; g0 += SPLIT ? 4 : 1) {
     int it, stage;
     if (SPLIT) {                                  // four tiles at a time, one a warp
 #pragma unroll 1
@@ -400,6 +407,25 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
       }
     }
     __syncthreads();
+    if (shared_out) {                             // this share's maximum, sum and raw output
+      if (warp == 0) {
+        const size_t at = ((size_t)b * nkv + g) * gridDim.x + blockIdx.x;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int r = (lane >> 2) + 8 * i;
+          if ((lane & 3) == 0) {
+            part_ml[(at * 16 + r) * 2] = m[i];
+            part_ml[(at * 16 + r) * 2 + 1] = l[i];
+          }
+#pragma unroll
+          for (int n = 0; n < DVT; ++n)
+            if (n * 8 < dv)
+              *reinterpret_cast<float2*>(part_o + (at * 16 + r) * dv + n * 8 + 2 * (lane & 3)) =
+                  make_float2(o[n][2 * i], o[n][2 * i + 1]);
+        }
+      }
+      return;
+    }
   }
   // the denominator (with the sink), the turn back, the gate, the store
 #pragma unroll
@@ -453,6 +479,68 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   }
 }
 
+// The shares of a row's keys (pwm_attention_kernel with scratch) made one: the maxima, sums and
+// raw outputs of the shares that exist for the request's position are combined in ascending
+// order, then the sink, the turn back and the gate as in the kernel's own epilogue.
+// grid (kv head, request); shares: how many the scratch has room for.
+__global__ void pwm_merge_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_ml, int shares,
+    const int* __restrict__ q_start, const int* __restrict__ positions,
+    const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+    const float* __restrict__ v_inv_freq, int interleaved, __nv_bfloat16* __restrict__ out,
+    int nh, int nkv, int dv, int window, int pool, int has_summary, int has_sink,
+    float sink_log2) {
+  __shared__ float wgt[32][16];                   // share x, row r: exp2(m_x - M) / L
+  const int g = blockIdx.x, b = blockIdx.y;
+  const int Gh = nh / nkv;
+  const int t0 = q_start[b], n_tok = q_start[b + 1] - t0;
+  const int rows_total = n_tok * Gh;
+  const int p_first = positions[t0];
+  const int p_hi = p_first + (rows_total - 1) / Gh;
+  const int nb_hi = (window > 0 && pool > 0 && has_summary && p_hi - window + 1 > 0)
+                        ? (p_hi - window + 1) / pool : 0;
+  const int j_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int n_tiles = (nb_hi + PWM_KEYS - 1) / PWM_KEYS + p_hi / PWM_KEYS - j_lo / PWM_KEYS + 1;
+  const int n_shares = min(shares, (n_tiles + 3) / 4);
+  const size_t at = ((size_t)b * nkv + g) * shares;
+  if (threadIdx.x < 16) {
+    const int r = threadIdx.x;
+    float M = has_sink ? sink_log2 : -1e30f;
+    for (int x = 0; x < n_shares; ++x) M = fmaxf(M, part_ml[((at + x) * 16 + r) * 2]);
+    float L = has_sink ? pwm_ex2(sink_log2 - M) : 0.f;
+    for (int x = 0; x < n_shares; ++x)
+      L += part_ml[((at + x) * 16 + r) * 2 + 1] * pwm_ex2(part_ml[((at + x) * 16 + r) * 2] - M);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int x = 0; x < n_shares; ++x)
+      wgt[x][r] = pwm_ex2(part_ml[((at + x) * 16 + r) * 2] - M) * inv;
+  }
+  __syncthreads();
+  const int half = dv >> 1;
+  for (int idx = threadIdx.x; idx < rows_total * half; idx += blockDim.x) {
+    const int r = idx / half, mi = idx - r * half;
+    const int tok = t0 + r / Gh, head = g * Gh + r % Gh;
+    const int iu = interleaved ? 2 * mi : mi, iv = interleaved ? 2 * mi + 1 : mi + half;
+    float u = 0.f, v = 0.f;
+    for (int x = 0; x < n_shares; ++x) {
+      const float* o = part_o + ((at + x) * 16 + r) * dv;
+      u += o[iu] * wgt[x][r];
+      v += o[iv] * wgt[x][r];
+    }
+    if (v_inv_freq) {
+      float sn, cs;
+      sincosf((float)(p_first + r / Gh) * v_inv_freq[mi], &sn, &cs);
+      const float a = u * cs + v * sn, c = v * cs - u * sn;
+      u = a;
+      v = c;
+    }
+    float gt = 1.f;
+    if (gate) gt = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)tok * gate_stride + head])));
+    __nv_bfloat16* dst = out + ((size_t)tok * nh + head) * dv;
+    dst[iu] = __float2bfloat16_rn(u * gt);
+    dst[iv] = __float2bfloat16_rn(v * gt);
+  }
+}
+
 // max_rows: the most rows (tokens x heads of a group) that one request brings to this step.
 BF_EXPORT int bf_pwm_attention(
     const void* q, const void* k_cache, const void* v_cache, const void* ks_cache,
@@ -461,7 +549,9 @@ BF_EXPORT int bf_pwm_attention(
     long long gate_stride, const float* v_inv_freq, int interleaved, void* out, int B,
     int max_tokens, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
     int s_page_size, int s_num_pages, int window, int pool, float scale, int has_sink,
-    float sink, int* err, cudaStream_t stream) {
+    float sink, float* part_o, float* part_ml, int shares, int* err, cudaStream_t stream) {
+  // part_o [B, nkv, shares, 16, dv], part_ml [B, nkv, shares, 16, 2] (float, or null): scratch
+  // for steps of single tokens, whose keys are then shared out over `shares` CTAs a row
   if (B <= 0 || max_tokens <= 0) return 0;
   if (dk % 16 || dv % 16 || dk > 128 || dv > 128 || nkv <= 0 || nh % nkv || nh / nkv > 64)
     return (int)cudaErrorInvalidValue;
@@ -470,6 +560,9 @@ BF_EXPORT int bf_pwm_attention(
   const int Gh = nh / nkv;
   dim3 grid((max_tokens * Gh + PWM_ROWS - 1) / PWM_ROWS, nkv, B);
   const bool split = max_tokens * Gh <= 16;       // single tokens: the keys shared out over warps
+  const bool multi = split && part_o && part_ml && shares > 1 && shares <= 32;
+  if (multi) grid.x = shares;
+  else part_o = part_ml = nullptr;
   size_t smem = (split ? 4 : 2) * (size_t)PWM_KEYS * ((dk + 8) + (dv + 8)) * sizeof(__nv_bfloat16);
   if (smem < (size_t)PWM_ROWS * dv * sizeof(float) + 512)
     smem = (size_t)PWM_ROWS * dv * sizeof(float) + 512;
@@ -488,6 +581,14 @@ BF_EXPORT int bf_pwm_attention(
       (const __nv_bfloat16*)ks_cache, (const __nv_bfloat16*)vs_cache, q_start, positions, tables,
       table_stride, s_tables, s_table_stride, (const __nv_bfloat16*)gate, gate_stride, v_inv_freq,
       interleaved, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, s_page_size,
-      s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, err);
+      s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, part_o, part_ml, err);
+  if (multi) {
+    const int e = bf_launch_status();
+    if (e) return e;
+    pwm_merge_kernel<<<dim3(nkv, B), 128, 0, stream>>>(
+        part_o, part_ml, shares, q_start, positions, (const __nv_bfloat16*)gate, gate_stride,
+        v_inv_freq, interleaved, (__nv_bfloat16*)out, nh, nkv, dv, window, pool,
+        ks_cache != nullptr, has_sink, sink * log2e);
+  }
   return bf_launch_status();
 }

@@ -556,10 +556,12 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   v_inv_freq: Optional[torch.Tensor], interleaved: bool, out: torch.Tensor,
                   B: int, max_tokens: int, nh: int, nkv: int, dk: int, dv: int,
                   window: Optional[int], pool: int, scale: float, sink: Optional[float],
-                  err: torch.Tensor) -> None:
+                  err: torch.Tensor, max_ctx: int = 0) -> None:
     """``apw_attention`` on the tensor cores (bfloat16; sizes: ``pwm_attention_takes``):
     request ``b`` of the batch owns the token rows ``q_start[b] .. q_start[b+1]-1``, at most
-    ``max_tokens`` of them."""
+    ``max_tokens`` of them.  ``max_ctx``: the longest context in the batch, if the caller
+    knows it: a step of single tokens then shares each row's key tiles out over several CTAs
+    (four tiles of 64 keys each) whose partial results a second kernel makes one."""
     if not pwm_attention_takes(q.dtype, nh, nkv, dk, dv):
         raise KernelError("pwm_attention: bfloat16, head sizes multiples of 16 up to 128")
     if not q.is_contiguous() or not out.is_contiguous() or q.data_ptr() % 16:
@@ -567,6 +569,19 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype):
         raise KernelError("pwm_attention: gate rows must be contiguous and of q's type")
     has_s = ks_cache is not None
+    part_o = part_ml = None
+    shares = 0
+    if max_ctx > 0 and max_tokens * (nh // nkv) <= 16:
+        span = (min(window, max_ctx) if window else max_ctx) + 16     # (+ the step's own tokens)
+        tiles = (span + 63) // 64 + 1
+        if has_s and window and pool:
+            tiles += (max(0, max_ctx - window) // pool + 63) // 64
+        shares = (tiles + 3) // 4
+        if 1 < shares <= 32:
+            part_o = torch.empty((B, nkv, shares, 16, dv), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((B, nkv, shares, 16, 2), dtype=torch.float32, device=q.device)
+        else:
+            shares = 0
     _run("pwm_attention", lib().bf_pwm_attention, _ptr(q), _ptr(k_cache), _ptr(v_cache),
          _ptr(ks_cache), _ptr(vs_cache), _ptr(q_start), _ptr(positions), _ptr(tables),
          _c_int(tables.stride(0)), _ptr(s_tables), _c_int(s_tables.stride(0) if has_s else 0),
@@ -575,7 +590,8 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
          _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
          _c_int(ks_cache.shape[2] if has_s else 1), _c_int(ks_cache.shape[0] if has_s else 0),
          _c_int(window or 0), _c_int(pool if has_s else 0), _c_float(scale),
-         _c_int(0 if sink is None else 1), _c_float(sink or 0.0), _ptr(err), _stream())
+         _c_int(0 if sink is None else 1), _c_float(sink or 0.0), _ptr(part_o), _ptr(part_ml),
+         _c_int(shares), _ptr(err), _stream())
 
 
 # ------------------------------------------------------------- matrix products

@@ -131,7 +131,7 @@ class PooledWindowAttention(Mixer):
                               ctx.block_tables[g], s_tables, gate, v_inv, s.interleaved, out,
                               ctx.B, 1 if ctx.decode_only else ctx.max_q_len, self.H, self.G,
                               self.dk, self.dv, s.window, self.pool, s.softmax_scale, s.sink,
-                              ctx.err)
+                              ctx.err, max_ctx=ctx.max_ctx_len)
             return linear(out, self.w_o)
         ops.apw_attention(q, view.k_cache, view.v_cache, ks, vs, ctx.seq_of_token, ctx.positions,
                           ctx.block_tables[g], s_tables, gate, v_inv, s.interleaved, out, self.H,

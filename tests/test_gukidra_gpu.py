@@ -181,20 +181,23 @@ def test_attention_sink_and_first_tokens(cuda_device, tmp_path):
     _compare(H.run_trace(_runner(d, torch.float32, 16, 2), steps), ref, torch.float32, "sink")
 
 
-def test_tensor_core_attention_beside_the_plain_kernel(cuda_device, tmp_path):
+@pytest.mark.parametrize("W,P,T,marked", [
+    (40, 8, 300, list(range(16, 24)) + [100, 139, 140, 250, 299]),
+    # long enough for single tokens to share their key tiles out over several CTAs
+    (200, 4, 520, list(range(16, 20)) + [250, 449, 450, 519])], ids=["short", "long"])
+def test_tensor_core_attention_beside_the_plain_kernel(cuda_device, tmp_path, W, P, T, marked):
     """bfloat16: the tiled tensor-core kernel (rows of a group's heads side by side, prompt
-    portions and single tokens) and the one-warp-per-row kernel give the same logits to
+    portions and single tokens, whose keys are shared out over warps and, in long contexts,
+    over CTAs with a merge) and the one-warp-per-row kernel give the same logits to
     rounding, on a case whose marked keys make a wrong mask show."""
     import importlib
     from binfer_b200.csrc import ops
     mod = importlib.import_module("binfer_b200.parts.attention_pooled")
-    W, P, T = 40, 8, 300
     mx = H._guk_attn(6, 2, 32, 48, W, P, 16, scale=0.4)
-    raw = _one_layer(H._guk_layer("attention", mx, 64), vocab=500, width=64)
-    toks = _distinct_tokens(T, 500, 33)
-    marked = list(range(16, 24)) + [100, 139, 140, 250, 299]
+    raw = _one_layer(H._guk_layer("attention", mx, 64), vocab=600, width=64)
+    toks = _distinct_tokens(T, 600, 33)
     d = H.make_gukidra_dir(tmp_path, "A", torch.bfloat16, raw=raw,
-                           tweak=_stand_out(raw, toks, marked), tag="tc")
+                           tweak=_stand_out(raw, toks, marked), tag=f"tc{T}")
     raw, w = H.read_model_dir(d)
     ref = {"a": G.forward(raw, w, toks)}
     outs = []
