@@ -33,7 +33,9 @@ class KVNeed:
     the keys behind its window); each P gets a *summary group* of its own, in which a
     request holds ``length // P`` entries.  A token's page is then kept until the token has
     left the window AND its block's mean is taken.  ``stride`` > 1 marks such a summary
-    group's own need (made by the manager, not by mixers)."""
+    group's own need (made by the manager, not by mixers).  ``keep_first``: with a window,
+    the request's first that many tokens stay visible for good, so the pages that hold them
+    are never given back while the request lives."""
 
     num_kv_heads: int
     head_dim: int
@@ -41,6 +43,7 @@ class KVNeed:
     value_dim: Optional[int] = None
     pools: Tuple[int, ...] = ()
     stride: int = 1
+    keep_first: int = 0
 
     @property
     def v_dim(self) -> int:
@@ -48,10 +51,16 @@ class KVNeed:
 
     @property
     def group_key(self) -> Tuple:
-        if self.value_dim is None and not self.pools and self.stride == 1:
+        if (self.value_dim is None and not self.pools and self.stride == 1
+                and not self.kept_tokens):
             return (self.num_kv_heads, self.head_dim, self.window)
         return (self.num_kv_heads, self.head_dim, self.window, self.v_dim, self.pools,
-                self.stride)
+                self.stride, self.kept_tokens)
+
+    @property
+    def kept_tokens(self) -> int:
+        """First tokens that stay behind the window (nothing without a window: all stay)."""
+        return int(self.keep_first) if self.window is not None else 0
 
     def merged(self, other: "KVNeed") -> "KVNeed":
         """The need of a cache that serves this execution and another that reads it: the
@@ -63,7 +72,8 @@ class KVNeed:
         window = (None if self.window is None or other.window is None
                   else max(self.window, other.window))
         pools = tuple(sorted(set(self.pools) | set(other.pools))) if window is not None else ()
-        return KVNeed(self.num_kv_heads, self.head_dim, window, self.value_dim, pools)
+        return KVNeed(self.num_kv_heads, self.head_dim, window, self.value_dim, pools,
+                      keep_first=max(self.kept_tokens, other.kept_tokens))
 
 
 @dataclass(frozen=True)
@@ -123,7 +133,8 @@ def plan_pages(kv_needs: Sequence[Optional[KVNeed]], page_size: int, budget_byte
             continue
         key = need.group_key
         tokens = max_seq_len if need.window is None else min(
-            max_seq_len, need.window + max(need.pools, default=0) + max_tokens_per_step)
+            max_seq_len, need.window + max(need.pools, default=0) + need.kept_tokens
+            + max_tokens_per_step)
         per_request[key] = -(-tokens // page_size) + 2
         page_bytes[key] = page_bytes.get(key, 0) + (
             need.num_kv_heads * (need.head_dim + need.v_dim) * page_size * element_size)
@@ -165,6 +176,12 @@ class CacheGroup:
         for P in self.need.pools:        # tokens of a block whose mean is not yet taken stay
             first_key = min(first_key, (length // P) * P)
         return first_key // self.page_size
+
+    @property
+    def kept_pages(self) -> int:
+        """Logical pages at a request's start that are never given back: those that hold
+        the first tokens a window keeps."""
+        return -(-self.need.kept_tokens // self.page_size)
 
     def entries_for(self, length: int) -> int:
         """Entries (tokens; blocks in a summary group) that a request of ``length`` tokens holds."""
@@ -247,7 +264,7 @@ class CacheManager:
             want = -(-g.entries_for(new_len) // g.page_size)
             add = max(0, want - len(table))
             first = g.first_needed_page(rc.length)
-            release = sum(1 for p in table[:first] if p > 0)
+            release = sum(1 for p in table[g.kept_pages:first] if p > 0)
             out.append(add - release)
         return out
 
@@ -290,7 +307,7 @@ class CacheManager:
 
     def _release_passed(self, g: CacheGroup, rc: RequestCache, table: List[int]) -> None:
         first = min(g.first_needed_page(rc.length), len(table))
-        for i in range(first):
+        for i in range(g.kept_pages, first):
             if table[i] > 0:
                 g.pool.free(table[i])
                 table[i] = -1
@@ -329,7 +346,8 @@ class CacheManager:
             if w is not None:
                 w += max(g.need.pools, default=0)
             m = g.entries_for(n)
-            need = -(-m // g.page_size) if w is None else -(-min(m, w + 1) // g.page_size) + 1
+            need = -(-m // g.page_size) if w is None else min(
+                -(-m // g.page_size), -(-min(m, w + 1) // g.page_size) + 1 + g.kept_pages)
             if need > g.pool.num_pages:
                 return False
         return True

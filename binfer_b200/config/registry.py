@@ -69,6 +69,8 @@ def _register_builtin() -> None:
     register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict)
     from .gukidra import GukidraConfig
     register_architecture("Gukidra", GukidraConfig.from_dict)
+    from .fikotar import FikotarConfig
+    register_architecture("Fikotar", FikotarConfig.from_dict)
 
 
 _register_builtin()

@@ -24,6 +24,21 @@ class RopeSpec:
     rotary_dim: int = 0          # 0 means the whole head
     # linear position scaling (angle = position / factor * inv_freq); 1.0 = none
     factor: float = 1.0
+    # scaling by wavelength: see WavelengthScaling; None = none
+    wavelength_scaling: Optional["WavelengthScaling"] = None
+
+
+@dataclass(frozen=True)
+class WavelengthScaling:
+    """Frequencies stretched by their wavelength ``l = 2 pi / f`` against a context length
+    ``original``: short waves (``l < original / high``) stay, long ones (``l > original /
+    low``) become ``f / factor``, and between the two, with ``s = (original / l - low) /
+    (high - low)``, ``(1 - s) f / factor + s f``."""
+
+    factor: float = 1.0
+    low: float = 1.0
+    high: float = 4.0
+    original: float = 8192.0
 
 
 @dataclass(frozen=True)
@@ -31,9 +46,11 @@ class NormSpec:
     """``offset``: what is added to the stored weight to get the one that multiplies (1.0 for
     a family whose norm weights hold the deviation from one)."""
 
-    kind: str = "rmsnorm"
+    kind: str = "rmsnorm"      # or "layernorm": mean taken off, weight and bias
     eps: float = 1e-6
     offset: float = 0.0
+    # layernorm: what follows the weight tensor's name to give the bias tensor's (None: no bias)
+    bias_suffix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -150,6 +167,100 @@ class MLSTMSpec:
 
 
 @dataclass(frozen=True)
+class ConvWindowAttentionSpec:
+    """Grouped-query softmax attention whose q, k and v projections pass a short causal
+    convolution over time, with a sliding window that keeps the request's first tokens.
+
+    Order: projection, convolution per channel (``conv_taps`` taps, 0 or 1: none), rotation of
+    q and k (``position``), each q and k head divided by its root mean square
+    (``unit_norm``, no weight, ``norm_eps``), scores ``(q . k) * scale``, the mask (position i
+    sees j <= i with ``i - j < window`` or ``j < keep_first``; ``window`` None: every j <= i),
+    softmax whose denominator also holds ``exp(sink_h)`` when ``sinks``, values of size
+    ``value_dim``, output projection.  ``names``: the tensors inside the mixer's prefix;
+    a convolution's tensor is the projection's name with ``conv_suffix``."""
+
+    kind: str = "conv_window_attention"
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 0
+    position: Optional[RopeSpec] = None
+    unit_norm: bool = True
+    norm_eps: float = 1e-6
+    scale: Optional[float] = None
+    window: Optional[int] = None
+    keep_first: int = 0
+    sinks: bool = False
+    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"),
+                                          ("sink", "sink"))
+    conv_suffix: str = ".conv"
+
+    @property
+    def softmax_scale(self) -> float:
+        return self.scale if self.scale is not None else self.head_dim ** -0.5
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head: ``S <- decay_h S + k v^T``, ``o = S^T q``
+    (no softmax, no denominator).  q and k are turned by ``position`` and k multiplied by
+    ``qk_dim ** -0.5``; each head's output is divided by its root mean square (``norm_eps``,
+    no weight), multiplied by ``silu`` of a gate projection and projected."""
+
+    kind: str = "retention"
+    num_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    decays: Tuple[float, ...] = ()
+    position: Optional[RopeSpec] = None
+    norm_eps: float = 1e-6
+    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("g", "g"),
+                                          ("o", "o"))
+
+
+@dataclass(frozen=True)
+class MixerBranch:
+    """One of the mixers that run side by side: its spec, the name that follows the
+    combined mixer's prefix (``left.``), and the factor of its output in the sum."""
+
+    spec: object = None
+    prefix: str = ""
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class ParallelMixersSpec:
+    """Several mixers that read the same input; the result is ``sum_i scale_i mixer_i(h)``."""
+
+    kind: str = "parallel_mixers"
+    branches: Tuple[MixerBranch, ...] = ()
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Mixture of gated feed-forward experts: each token runs the ``top`` experts with the
+    largest router logits, weighted by the softmax over those logits alone.  A shared expert
+    (``shared_size`` > 0) runs for every token, multiplied by the sigmoid of a projection of
+    its own to one number when ``shared_gate``.  Names inside the feed-forward's prefix:
+    ``expert_prefix.format(e=...)`` and ``shared_prefix`` before ``names`` (gate, up, down);
+    ``router_name``; ``shared_gate_name`` inside the shared expert's prefix."""
+
+    kind: str = "moe"
+    num_experts: int = 0
+    top: int = 0
+    expert_size: int = 0
+    shared_size: int = 0
+    shared_gate: bool = False
+    activation: str = "silu"
+    names: Tuple[str, str, str] = ("gate", "up", "down")
+    expert_prefix: str = "e{e}."
+    shared_prefix: str = "shared."
+    router_name: str = "router"
+    shared_gate_name: str = "sg"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One decoder layer: which mixer, which feed-forward, which norm, how arranged."""
 
@@ -157,7 +268,9 @@ class LayerSpec:
     ffn: object = None           # a feed-forward spec with a ``kind`` attribute (None: the
                                  # arrangement has no second sublayer in this layer)
     norm: NormSpec = NormSpec()
-    block: str = "prenorm"       # arrangement of the parts inside the layer
+    block: str = "prenorm"       # arrangement of the parts inside the layer: "prenorm",
+                                 # "sublayer_norm", or "parallel" (one norm, both sublayers
+                                 # read it, their sum is added)
 
 
 @dataclass(frozen=True)

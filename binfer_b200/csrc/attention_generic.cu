@@ -19,6 +19,12 @@
 // kernels take none): a soft cap s <- c tanh(s / c), a bias per distance s <- s +
 // slope_h (j - p), and a sink, a logit per head that joins the softmax's denominator and
 // carries no value.  All three are off with softcap 0 and null pointers.
+//
+// Two more things that the tuned kernels do not take: values of another size than keys
+// (`dv`), and a window that keeps the request's first tokens: with keep_first > 0 the keys
+// j < keep_first stay visible behind the window, at their true positions.  They are walked
+// first, again in tiles of 32 counted from position 0.  `out_stride` and `out_scale` let the
+// result land, scaled, in a column block of a wider buffer.
 #include <float.h>
 
 #include "common.cuh"
@@ -31,7 +37,8 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ block_tables, int table_stride, A* __restrict__ out, int nh, int nkv,
     int d, int page_size, int num_pages, int window, float scale, float softcap,
-    const float* __restrict__ slopes, const float* __restrict__ sinks, int* __restrict__ err) {
+    const float* __restrict__ slopes, const float* __restrict__ sinks, int* __restrict__ err,
+    int dv, int keep_first, long long q_stride, long long out_stride, float out_scale) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -40,7 +47,7 @@ __global__ void paged_attention_generic_kernel(
   if (h >= nh) return;
   const int g = h / (nh / nkv);
   float* qs = sh + (size_t)warp * d;
-  const A* qrow = q + ((size_t)t * nh + h) * d;
+  const A* qrow = q + (size_t)t * q_stride + (size_t)h * d;
   for (int i = lane; i < d; i += 32) qs[i] = bf_ld(qrow + i) * scale;
   __syncwarp();
 
@@ -53,10 +60,17 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
   for (int c = 0; c < ATT_MAX_ACC; ++c) acc[c] = 0.f;
 
-  for (int tile = j0 >> 5; tile <= (p >> 5); ++tile) {
+  // the kept first tokens that the window no longer covers, then the window
+  const int kept = window > 0 ? min(keep_first, j0) : 0;
+  const int kept_tiles = (kept + 31) >> 5;
+  const int first_tile = j0 >> 5;
+  const int n_tiles = kept_tiles + (p >> 5) - first_tile + 1;
+  for (int it = 0; it < n_tiles; ++it) {
+    const bool in_kept = it < kept_tiles;
+    const int tile = in_kept ? it : first_tile + (it - kept_tiles);
     const int j = (tile << 5) + lane;
-    bool valid = j >= j0 && j <= p;
-    long long row = 0;     // element offset of this lane's key/value row
+    bool valid = in_kept ? j < kept : (j >= j0 && j <= p);
+    long long row = 0;     // index of this lane's key/value row (in rows of the cache)
     if (valid) {
       const int lp = j / page_size;
       const int page = table[lp];
@@ -64,12 +78,12 @@ __global__ void paged_attention_generic_kernel(
         atomicOr(err, BF_ERR_PAGE);
         valid = false;
       } else {
-        row = (((long long)page * nkv + g) * page_size + (j - lp * page_size)) * d;
+        row = ((long long)page * nkv + g) * page_size + (j - lp * page_size);
       }
     }
     float s = -FLT_MAX;
     if (valid) {
-      const A* kr = k_cache + row;
+      const A* kr = k_cache + row * d;
       float a = 0.f;
 #pragma unroll 8
       for (int i = 0; i < d; ++i) a += qs[i] * bf_ld(kr + i);
@@ -89,11 +103,11 @@ __global__ void paged_attention_generic_kernel(
       if (!((live >> jj) & 1u)) continue;
       const float pb = __shfl_sync(0xffffffffu, pj, jj);
       const long long rb = __shfl_sync(0xffffffffu, row, jj);
-      const A* vr = v_cache + rb;
+      const A* vr = v_cache + rb * dv;
 #pragma unroll
       for (int c = 0; c < ATT_MAX_ACC; ++c) {
         const int i = lane + 32 * c;
-        if (i < d) acc[c] += pb * bf_ld(vr + i);
+        if (i < dv) acc[c] += pb * bf_ld(vr + i);
       }
     }
   }
@@ -104,12 +118,12 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
     for (int c = 0; c < ATT_MAX_ACC; ++c) acc[c] *= corr;
   }
-  const float inv = 1.f / l;
-  A* o = out + ((size_t)t * nh + h) * d;
+  const float inv = out_scale / l;
+  A* o = out + (size_t)t * out_stride + (size_t)h * dv;
 #pragma unroll
   for (int c = 0; c < ATT_MAX_ACC; ++c) {
     const int i = lane + 32 * c;
-    if (i < d) bf_st(o + i, acc[c] * inv);
+    if (i < dv) bf_st(o + i, acc[c] * inv);
   }
 }
 
@@ -117,9 +131,11 @@ BF_EXPORT int bf_paged_attention_generic(
     const void* q, const void* k_cache, const void* v_cache, const int* seq_of_token,
     const int* positions, const int* block_tables, int table_stride, void* out, int T, int nh,
     int nkv, int d, int page_size, int num_pages, int window, float scale, float softcap,
-    const float* slopes, const float* sinks, int act_dtype, int* err, cudaStream_t stream) {
+    const float* slopes, const float* sinks, int act_dtype, int* err, int dv, int keep_first,
+    long long q_stride, long long out_stride, float out_scale, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (d > 32 * ATT_MAX_ACC || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+  if (d > 32 * ATT_MAX_ACC || dv > 32 * ATT_MAX_ACC || nkv <= 0 || nh % nkv)
+    return (int)cudaErrorInvalidValue;
   const int warps = 4;
   dim3 grid(T, (nh + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
@@ -127,11 +143,11 @@ BF_EXPORT int bf_paged_attention_generic(
     paged_attention_generic_kernel<float><<<grid, warps * 32, smem, stream>>>(
         (const float*)q, (const float*)k_cache, (const float*)v_cache, seq_of_token, positions,
         block_tables, table_stride, (float*)out, nh, nkv, d, page_size, num_pages, window, scale,
-        softcap, slopes, sinks, err);
+        softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale);
   else
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         seq_of_token, positions, block_tables, table_stride, (__nv_bfloat16*)out, nh, nkv, d,
-        page_size, num_pages, window, scale, softcap, slopes, sinks, err);
+        page_size, num_pages, window, scale, softcap, slopes, sinks, err, dv, keep_first, q_stride, out_stride, out_scale);
   return bf_launch_status();
 }

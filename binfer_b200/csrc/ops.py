@@ -221,13 +221,21 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             d: int, window: Optional[int], scale: float,
                             err: torch.Tensor, softcap: float = 0.0,
                             slopes: Optional[torch.Tensor] = None,
-                            sinks: Optional[torch.Tensor] = None) -> None:
+                            sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
+                            keep_first: int = 0, out_scale: float = 1.0) -> None:
     """Attention of every token row over its request's pages, any sizes.  ``softcap``,
     ``slopes`` (float32 ``[nh]``) and ``sinks`` (float32 ``[nh]``) change the scores as
-    ``config.specs.ScoreSpec`` says; by default nothing is changed."""
+    ``config.specs.ScoreSpec`` says; by default nothing is changed.  ``value_dim``: size of a
+    value head where it differs from ``d``.  ``keep_first``: with a window, the request's
+    first that many tokens stay visible behind it.  ``q`` and ``out`` may be column blocks of
+    wider buffers (rows ``nh * d`` and ``nh * value_dim`` long); ``out_scale`` multiplies the
+    result."""
     T = q.shape[0]
-    if d > 256:
-        raise KernelError(f"attention: head_dim {d} is not supported (at most 256)")
+    dv = d if value_dim is None else int(value_dim)
+    if d > 256 or dv > 256:
+        raise KernelError(f"attention: head sizes {d}, {dv} are not supported (at most 256)")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention: rows of q and out must be contiguous")
     for name, t in (("slopes", slopes), ("sinks", sinks)):
         if t is not None:
             _want(t, torch.float32, name)
@@ -238,7 +246,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(T), _c_int(nh),
         _c_int(nkv), _c_int(d), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
         _c_int(window or 0), _c_float(scale), _c_float(softcap), _ptr(slopes), _ptr(sinks),
-        _c_int(_dtype_code(q)), _ptr(err), _stream())
+        _c_int(_dtype_code(q)), _ptr(err), _c_int(dv), _c_int(keep_first), _c_ll(q.stride(0)),
+        _c_ll(out.stride(0)), _c_float(out_scale), _stream())
 
 
 DECODE_HEAD_DIMS = (32, 64, 96, 128, 256)
@@ -391,6 +400,173 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
          _ptr(block_tables), _c_int(block_tables.stride(0)), _ptr(out), _c_int(nh), _c_int(nkv),
          _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]), _c_int(window or 0),
          _c_float(scale), _ptr(err), _stream())
+
+
+# ------------------------------------------------------------------ layer norm
+def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor],
+                  delta2: Optional[torch.Tensor], weight: torch.Tensor,
+                  bias: Optional[torch.Tensor], out: torch.Tensor, eps: float,
+                  rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+    """out[i] = layernorm(resid[r] + delta[r] + delta2[r]) * weight + bias with r = rows[i]
+    (or i); the sum is written back to resid when ``write_back``."""
+    _want(resid, torch.float32, "resid"); _want(weight, torch.float32, "weight")
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+    n, H = out.shape
+    for d in (delta, delta2):
+        if d is not None and (d.dtype != out.dtype or not d.is_contiguous()
+                              or d.shape != resid.shape):
+            raise KernelError("a delta must be contiguous, of the stream's shape and of the "
+                              "output's dtype")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    _run("add_layernorm", lib().bf_add_layernorm, _ptr(resid), _ptr(delta), _ptr(delta2),
+         _ptr(weight), _ptr(bias), _ptr(out), _ptr(rows), _c_int(n), _c_int(H), _c_float(eps),
+         _c_int(_dtype_code(out)), _c_int(1 if write_back else 0), _stream())
+
+
+# --------------------------------- projections that pass a short convolution over time
+CONV_MAX_TAPS = 8
+
+
+def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
+                state: Optional[torch.Tensor], state_slots: torch.Tensor,
+                seq_of_token: torch.Tensor, q_start: torch.Tensor,
+                inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                slots: Optional[torch.Tensor], q_out: torch.Tensor,
+                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], nh: int,
+                nkv: int, dk: int, dv: int, unit_norm: bool, eps: float,
+                err: torch.Tensor) -> None:
+    """``proj`` rows hold ``[q: nh dk | k: nkv dk | v: nkv dv]`` (a column block of a wider
+    buffer is fine).  Per channel a causal convolution over the request's tokens with
+    ``conv_w`` float32 ``[channels, taps]`` (``taps`` <= 1: none), whose reach behind the
+    step's first row is read from ``state`` float32 ``[slots, (taps-1) * channels]`` (a column
+    block of the slots' storage); then q and k turned by the position (``inv_freq``), each
+    head of them divided by its root mean square when ``unit_norm``; q to ``q_out``, k and v
+    into the pages at ``slots``.  The state is not changed: see :func:`conv_state_shift`."""
+    T = proj.shape[0]
+    C = nh * dk + nkv * (dk + dv)
+    if proj.stride(1) != 1 or proj.shape[1] != C or q_out.stride(1) != 1:
+        raise KernelError("conv_encode: proj must be [T, nh dk + nkv (dk + dv)] with contiguous rows")
+    if taps > CONV_MAX_TAPS:
+        raise KernelError(f"conv_encode: at most {CONV_MAX_TAPS} taps")
+    if taps > 1:
+        _want(conv_w, torch.float32, "conv_w")
+        if tuple(conv_w.shape) != (C, taps):
+            raise KernelError("conv_encode: conv_w must be [channels, taps]")
+        if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] != (taps - 1) * C:
+            raise KernelError("conv_encode: state must be float32 [slots, (taps-1) * channels]")
+    if inv_freq is not None:
+        _want(inv_freq, torch.float32, "inv_freq")
+    rot_half = 0 if inv_freq is None else inv_freq.numel()
+    if 2 * rot_half > dk:
+        raise KernelError("conv_encode: more rotated sizes than a head has")
+    page_size = k_cache.shape[2] if k_cache is not None else 1
+    num_slots = k_cache.shape[0] * page_size if k_cache is not None else 0
+    if k_cache is not None and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError("cache pages must be contiguous")
+    _run("conv_encode", lib().bf_conv_encode, _ptr(proj), _c_ll(proj.stride(0)), _ptr(conv_w),
+         _c_int(taps), _ptr(state), _c_ll(state.stride(0) if state is not None else 0),
+         _ptr(state_slots), _c_int(state.shape[0] if state is not None else 0),
+         _ptr(seq_of_token), _ptr(q_start), _ptr(inv_freq), _c_int(rot_half), _ptr(positions),
+         _ptr(slots), _ptr(q_out), _c_ll(q_out.stride(0)), _ptr(k_cache), _ptr(v_cache), _c_int(T),
+         _c_int(nh), _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(page_size), _c_ll(num_slots),
+         _c_int(1 if unit_norm else 0), _c_float(eps), _c_int(_dtype_code(proj)), _ptr(err),
+         _stream())
+
+
+def conv_state_shift(proj: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor,
+                     q_start: torch.Tensor, B: int, taps: int) -> None:
+    """After :func:`conv_encode`: every request's state becomes the projected values of its
+    last ``taps - 1`` tokens (old rows stay where the step brought fewer)."""
+    C = proj.shape[1]
+    if taps <= 1:
+        return
+    if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] != (taps - 1) * C:
+        raise KernelError("conv_state_shift: state must be float32 [slots, (taps-1) * channels]")
+    _run("conv_state_shift", lib().bf_conv_state_shift, _ptr(proj), _c_ll(proj.stride(0)),
+         _ptr(state), _c_ll(state.stride(0)), _ptr(state_slots), _c_int(state.shape[0]),
+         _ptr(q_start), _c_int(B), _c_int(C), _c_int(taps), _c_int(_dtype_code(proj)), _stream())
+
+
+# ------------------------------------------------------------------------- retention
+RETENTION_MAX_QK_DIM = 1024
+
+
+def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decays: torch.Tensor,
+                   inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                   state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor,
+                   o_raw: torch.Tensor, B: int, heads: int, dk: int, dv: int, k_scale: float,
+                   err: torch.Tensor) -> None:
+    """The recurrence ``S <- decay_h S + k v^T, o = S^T q`` over every request's tokens of the
+    step.  ``proj`` rows hold q (``heads dk`` numbers from column ``q_off``), k (from
+    ``k_off``) and v (``heads dv`` from ``v_off``); q and k are turned by the position
+    (``inv_freq`` float32, None: not) and k multiplied by ``k_scale``.  ``state`` float32
+    ``[slots, heads * dv * dk]`` (a column block of the slots' storage); ``o_raw`` float32
+    ``[T, heads dv]``."""
+    _want(decays, torch.float32, "decays"); _want(o_raw, torch.float32, "o_raw")
+    if proj.stride(1) != 1 or dk > RETENTION_MAX_QK_DIM:
+        raise KernelError(f"retention_scan: contiguous rows and a key size of at most "
+                          f"{RETENTION_MAX_QK_DIM}")
+    if (state.dtype != torch.float32 or state.stride(1) != 1
+            or state.shape[1] != heads * dk * dv or decays.numel() != heads):
+        raise KernelError("retention_scan: state must be float32 [slots, heads * dk * dv] and "
+                          "decays [heads]")
+    rot_half = 0 if inv_freq is None else inv_freq.numel()
+    if 2 * rot_half > dk:
+        raise KernelError("retention_scan: more rotated sizes than a head has")
+    _run("retention_scan", lib().bf_retention_scan, _ptr(proj), _c_ll(proj.stride(0)),
+         _c_ll(q_off), _c_ll(k_off), _c_ll(v_off), _ptr(decays), _ptr(inv_freq), _c_int(rot_half),
+         _ptr(positions), _ptr(state), _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots),
+         _c_int(state.shape[0]), _ptr(o_raw), _c_int(B), _c_int(heads), _c_int(dk), _c_int(dv),
+         _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err), _stream())
+
+
+def retention_out(o_raw: torch.Tensor, proj: torch.Tensor, g_off: int, out: torch.Tensor,
+                  heads: int, dv: int, eps: float, out_scale: float = 1.0) -> None:
+    """``out = o_raw / rms_per_head(o_raw) * silu(proj[:, g_off:]) * out_scale``; ``out`` may be
+    a column block of a wider buffer."""
+    _want(o_raw, torch.float32, "o_raw")
+    T = o_raw.shape[0]
+    if out.stride(1) != 1 or out.dtype != proj.dtype or proj.stride(1) != 1:
+        raise KernelError("retention_out: rows must be contiguous, out of the projection's type")
+    _run("retention_out", lib().bf_retention_out, _ptr(o_raw), _ptr(proj), _c_ll(proj.stride(0)),
+         _c_ll(g_off), _ptr(out), _c_ll(out.stride(0)), _c_int(T), _c_int(heads), _c_int(dv),
+         _c_float(eps), _c_float(out_scale), _c_int(_dtype_code(proj)), _stream())
+
+
+# ---------------------------------------------------------------- mixture of experts
+def moe_route(h: torch.Tensor, w: torch.Tensor, experts: int, top: int, shared_gate: bool,
+              route_w: torch.Tensor, top_ids: torch.Tensor, top_w: torch.Tensor) -> None:
+    """Router of a mixture of experts: ``w`` float32 ``[experts (+1), width]`` (the last row the
+    shared expert's gate when ``shared_gate``), ``h [T, width]``.  ``route_w`` float32
+    ``[T, experts (+1)]`` gets every expert's weight for the token (zero: not chosen; the
+    last column ``sigmoid(w_sg . h)``), ``top_ids`` int32 and ``top_w`` float32 ``[T, top]``
+    the chosen experts, largest logit first."""
+    T, width = h.shape
+    rows = experts + (1 if shared_gate else 0)
+    _want(w, torch.float32, "w"); _want(route_w, torch.float32, "route_w")
+    _want(top_ids, torch.int32, "top_ids"); _want(top_w, torch.float32, "top_w")
+    if tuple(w.shape) != (rows, width) or tuple(route_w.shape) != (T, rows) or h.stride(1) != 1:
+        raise KernelError("moe_route: w must be [experts (+1), width], route_w [T, experts (+1)]")
+    _run("moe_route", lib().bf_moe_route, _ptr(h), _c_ll(h.stride(0)), _ptr(w), _c_int(T),
+         _c_int(width), _c_int(experts), _c_int(top), _c_int(1 if shared_gate else 0),
+         _ptr(route_w), _ptr(top_ids), _ptr(top_w), _c_int(_dtype_code(h)), _stream())
+
+
+def moe_act(gu: torch.Tensor, route_w: torch.Tensor, act: torch.Tensor, experts: int,
+            ff: int) -> None:
+    """``act[t, c] = silu(gu[t, c]) * gu[t, F + c] * route_w[t, expert(c)]`` with
+    ``expert(c) = c // ff`` for ``c < experts * ff`` and the column behind the experts' for the
+    rest (weight one if ``route_w`` has no such column)."""
+    T, F = act.shape
+    _want(route_w, torch.float32, "route_w")
+    if tuple(gu.shape) != (T, 2 * F) or not gu.is_contiguous() or not act.is_contiguous() \
+            or gu.dtype != act.dtype or route_w.shape[0] != T:
+        raise KernelError("moe_act: gu must be contiguous [T, 2 F] of act's type")
+    _run("moe_act", lib().bf_moe_act, _ptr(gu), _ptr(route_w), _ptr(act), _c_int(T), _c_int(F),
+         _c_int(experts), _c_int(ff), _c_int(route_w.shape[1]), _c_int(_dtype_code(act)),
+         _stream())
 
 
 # ----------------------------------------------------- norm on a sublayer's output

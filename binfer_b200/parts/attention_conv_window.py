@@ -1,0 +1,129 @@
+"""Softmax attention whose projections pass a short convolution, with a window that keeps
+the request's first tokens, as a mixer part.
+
+Order of operations: one product for q, k and v; a causal convolution over time on every
+channel of the three (the projected values of a request's last ``taps - 1`` tokens are
+per-request state, so a prompt can be cut anywhere); rotation of q and k; each q and k head
+divided by its root mean square, after the rotation; k and v into the pages; attention in
+which position i sees j <= i with ``i - j < window`` or ``j < keep_first`` (kept tokens stay
+at their true positions) and whose softmax has a learned logit per head in its denominator;
+the output projection.  Every key, also those of the step's own tokens, is read from the
+pages, so portions can share a step with decoded tokens.
+
+The mixer can run alone (``forward``) or as a branch of ``ParallelMixers``, which stacks the
+branches' input and output projections into one product each: ``w_in`` / ``w_out`` and
+``run(proj, ctx, view, out, out_scale)`` are that interface.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+
+from ..cache.manager import KVNeed, StateNeed
+from ..config.specs import ConvWindowAttentionSpec
+from ..csrc import ops
+from ..weights.loader import ParamSpec
+from .base import BuildEnv, EntryView, Mixer, StepContext, build_position, register_mixer
+from .linear import linear
+
+
+class ConvWindowAttention(Mixer):
+    def __init__(self, spec: ConvWindowAttentionSpec, hidden_size: int, prefix: str,
+                 env: BuildEnv):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if spec.head_dim > 256 or spec.value_dim > 256:
+            raise ValueError(f"head sizes {spec.head_dim}, {spec.value_dim} are not supported "
+                             f"(at most 256)")
+        if spec.conv_taps > ops.CONV_MAX_TAPS:
+            raise ValueError(f"a convolution of {spec.conv_taps} taps is not supported "
+                             f"(at most {ops.CONV_MAX_TAPS})")
+        self.spec, self.hidden, self.prefix, self.env = spec, hidden_size, prefix, env
+        self.H, self.G, self.dk, self.dv = (spec.num_heads, spec.num_kv_heads, spec.head_dim,
+                                            spec.value_dim)
+        self.q_size, self.k_size, self.v_size = self.H * self.dk, self.G * self.dk, self.G * self.dv
+        self.channels = self.q_size + self.k_size + self.v_size
+        self.taps = spec.conv_taps if spec.conv_taps > 1 else 0
+        self.position = (build_position(spec.position, self.dk, env)
+                         if spec.position is not None else None)
+        if self.position is not None and self.position.inv_freq is None:
+            raise ValueError("this attention takes rotary encodings only")
+        self.names = dict(spec.names)
+        self.in_rows, self.out_cols = self.channels, self.H * self.dv
+        self.w_in = self.w_out = self.conv_w = self.sinks = None
+
+    # ----------------------------------------------------------------- weights
+    def _spec(self, role: str) -> ParamSpec:
+        base = {"q": (self.q_size, self.hidden), "k": (self.k_size, self.hidden),
+                "v": (self.v_size, self.hidden), "o": (self.hidden, self.H * self.dv)}
+        if role in base:
+            return ParamSpec(self.prefix + self.names[role], base[role])
+        if role == "sink":
+            return ParamSpec(self.prefix + self.names["sink"], (self.H,), init="around_zero",
+                             role="vector")
+        src = role[:-5]                          # "q.conv" -> q
+        return ParamSpec(self.prefix + self.names[src] + self.spec.conv_suffix,
+                         (base[src][0], self.taps), init="conv", role="vector")
+
+    def _roles(self) -> List[str]:
+        roles = ["q", "k", "v", "o"]
+        if self.taps:
+            roles += ["q.conv", "k.conv", "v.conv"]
+        if self.spec.sinks:
+            roles.append("sink")
+        return roles
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [self._spec(r) for r in self._roles()]
+
+    def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
+        g = lambda role: get(self._spec(role))          # noqa: E731
+        self.w_in = torch.cat([g("q"), g("k"), g("v")], dim=0).contiguous()
+        self.w_out = g("o")
+        if self.taps:
+            self.conv_w = torch.cat([g("q.conv"), g("k.conv"), g("v.conv")], dim=0).contiguous()
+        if self.spec.sinks:
+            self.sinks = g("sink")
+
+    # ------------------------------------------------------------ cache, state
+    def kv_need(self) -> Optional[KVNeed]:
+        s = self.spec
+        return KVNeed(self.G, self.dk, s.window, None if self.dv == self.dk else self.dv,
+                      keep_first=s.keep_first if s.window is not None else 0)
+
+    def state_need(self) -> Optional[StateNeed]:
+        if not self.taps:
+            return None
+        return StateNeed(((self.taps - 1) * self.channels,), "float32")
+
+    # ----------------------------------------------------------------- forward
+    def forward(self, x: torch.Tensor, ctx: StepContext, view: EntryView) -> torch.Tensor:
+        out = torch.empty((x.shape[0], self.out_cols), dtype=x.dtype, device=x.device)
+        self.run(linear(x, self.w_in), ctx, view, out, 1.0)
+        return linear(out, self.w_out)
+
+    def run(self, proj: torch.Tensor, ctx: StepContext, view: EntryView, out: torch.Tensor,
+            out_scale: float) -> None:
+        """From the projections ``proj [T, channels]`` to the heads' outputs times
+        ``out_scale`` in ``out [T, heads * value_dim]`` (both may be column blocks)."""
+        s, T, g = self.spec, proj.shape[0], view.group
+        if not view.writes_cache:
+            raise ValueError("this attention keeps a cache of its own")
+        q = torch.empty((T, self.q_size), dtype=proj.dtype, device=proj.device)
+        inv = self.position.inv_freq if self.position is not None else None
+        state = view.state if self.taps else None
+        ops.conv_encode(proj, self.conv_w, self.taps, state, ctx.state_slots, ctx.seq_of_token,
+                        ctx.q_start, inv, ctx.positions, ctx.slots[g], q, view.k_cache,
+                        view.v_cache, self.H, self.G, self.dk, self.dv, s.unit_norm, s.norm_eps,
+                        ctx.err)
+        if self.taps:
+            ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
+        ops.paged_attention_generic(
+            q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, ctx.block_tables[g],
+            out, self.H, self.G, self.dk, s.window, s.softmax_scale, ctx.err, sinks=self.sinks,
+            value_dim=self.dv, keep_first=s.keep_first if s.window is not None else 0,
+            out_scale=out_scale)
+
+
+register_mixer("conv_window_attention", ConvWindowAttention)

@@ -209,6 +209,7 @@ class ResidualStream:
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.pending2: Optional[torch.Tensor] = None     # see add_pair
         self.ready: Optional[ScaledRows] = None
         self.ready_for = None
         # the stream itself in the activation type, for sublayers that read it without a
@@ -216,11 +217,31 @@ class ResidualStream:
         self.reading: Optional[torch.Tensor] = None
 
     def add(self, delta: torch.Tensor) -> None:
-        if self.pending is not None:
+        if self.pending is not None or self.pending2 is not None:
             self.flush()
         self.pending = delta
         self.ready = self.ready_for = None
         self.reading = None
+
+    def add_pair(self, a: torch.Tensor, b: torch.Tensor) -> None:
+        """Two sublayer outputs at once (sublayers that ran side by side on one norm's
+        output).  A norm that takes a second delta (``forward(..., also=)``) folds both in
+        one pass; before any other reader :meth:`flush` adds them."""
+        self.add(a)
+        self.pending2 = b
+
+    def norm_input(self, norm, rows: Optional[torch.Tensor] = None, n_rows: int = 0):
+        """``norm`` over the stream with everything pending folded in."""
+        if self.pending2 is not None:
+            if getattr(norm, "takes_second_delta", False):
+                also, self.pending2 = self.pending2, None
+                if rows is not None:
+                    return norm.forward(self, rows=rows, n_rows=n_rows, also=also)
+                return norm.forward(self, also=also)
+            self.flush()
+        if rows is not None:
+            return norm.forward(self, rows=rows, n_rows=n_rows)
+        return norm.forward(self)
 
     def read(self, dtype: torch.dtype) -> torch.Tensor:
         """The stream as a sublayer's products take it: itself in a float engine, else a copy
@@ -252,10 +273,13 @@ class ResidualStream:
         self.add(d.compute())
 
     def flush(self) -> None:
+        from ..csrc import ops
         if self.pending is not None:
-            from ..csrc import ops
             ops.residual_add(self.x, self.pending)
             self.pending = None
+        if self.pending2 is not None:
+            ops.residual_add(self.x, self.pending2)
+            self.pending2 = None
 
 
 # ------------------------------------------------------------------ registries

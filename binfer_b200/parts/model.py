@@ -28,6 +28,11 @@ from . import attention as _attention  # noqa: F401
 from . import attention_pooled as _attention_pooled  # noqa: F401
 from . import block as _block          # noqa: F401
 from . import block_sublayer_norm as _block_sublayer_norm  # noqa: F401
+from . import block_parallel as _block_parallel  # noqa: F401
+from . import attention_conv_window as _attention_conv_window  # noqa: F401
+from . import retention as _retention  # noqa: F401
+from . import mixers_parallel as _mixers_parallel  # noqa: F401
+from . import moe as _moe              # noqa: F401
 from . import mlstm as _mlstm          # noqa: F401
 from . import mlp as _mlp              # noqa: F401
 from . import norms as _norms          # noqa: F401
@@ -145,7 +150,7 @@ class DecoderModel:
         if R == 0:
             stream.flush()
             return torch.empty((0, spec.vocab_size), dtype=torch.float32, device=self.env.device)
-        y = self.final_norm.forward(stream, rows=ctx.logit_rows, n_rows=R)
+        y = stream.norm_input(self.final_norm, rows=ctx.logit_rows, n_rows=R)
         logits = linear(y, self.lm_head, out_dtype=torch.float32)
         if spec.logit_scale != 1.0:
             logits.mul_(spec.logit_scale)

@@ -44,6 +44,8 @@ class RMSNorm(Norm):
         if rows is None and stream.ready_for is self:
             out, stream.ready, stream.ready_for = stream.ready, None, None
             return out           # ScaledRows: the product before already prepared this norm
+        if stream.pending2 is not None:
+            stream.flush()       # a pair of adds: this norm's kernel folds one only
         stream.ready = stream.ready_for = None
         n = n_rows if rows is not None else stream.x.shape[0]
         out = torch.empty((n, self.size), dtype=self.env.dtype, device=self.env.device)
@@ -74,3 +76,47 @@ class RMSNorm(Norm):
 
 
 register_norm("rmsnorm", RMSNorm)
+
+
+class LayerNorm(Norm):
+    takes_second_delta = True      # forward(..., also=): see ResidualStream.add_pair
+
+    """``y = (x - mean) / sqrt(var + eps) * w + b`` with the variance the mean of the squared
+    deviations; the bias tensor is the weight's name with ``NormSpec.bias_suffix`` (None: no
+    bias).  Folds the stream's pending add, and a second one (``also``), into the same pass."""
+
+    def __init__(self, spec: NormSpec, size: int, name: str, env: BuildEnv):
+        self.eps = float(spec.eps)
+        self.size, self.name, self.env = size, name, env
+        self.bias_name = None if spec.bias_suffix is None else name + spec.bias_suffix
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        specs = [ParamSpec(self.name, (self.size,), init="norm", role="vector")]
+        if self.bias_name is not None:
+            specs.append(ParamSpec(self.bias_name, (self.size,), init="around_zero",
+                                   role="vector"))
+        return specs
+
+    def load(self, get: Callable[[ParamSpec], torch.Tensor]) -> None:
+        specs = self.param_specs()
+        self.weight = get(specs[0])
+        self.bias = get(specs[1]) if len(specs) > 1 else None
+
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
+                n_rows: int = 0, also: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Normed activations of every row, or of ``rows`` only (the stream is then left as it
+        is).  ``also``: one more sublayer output to add beside the pending one."""
+        stream.ready = stream.ready_for = None
+        n = n_rows if rows is not None else stream.x.shape[0]
+        out = torch.empty((n, self.size), dtype=self.env.dtype, device=self.env.device)
+        ops.add_layernorm(stream.x, stream.pending, also, self.weight, self.bias, out, self.eps,
+                          rows=rows, write_back=rows is None)
+        if rows is None:
+            stream.pending = None
+            stream.reading = None
+        return out
+
+
+register_norm("layernorm", LayerNorm)

@@ -7,9 +7,12 @@ cuda/kernels/bf16_kernels.cu:133-185).  The reference builds a cos/sin table for
 4096 positions on the host and truncates it to bfloat16
 (src/tensor/tensor.ts:136-145); here only the ``rot/2`` frequencies are kept, in
 float32, and the kernel forms the angle and its sine and cosine in float32, so
-no position limit and no table precision enter.
+no position limit and no table precision enter.  ``RopeSpec.wavelength_scaling``
+stretches the long waves (``config.specs.WavelengthScaling``).
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -27,6 +30,16 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = rot
         i = torch.arange(rot // 2, dtype=torch.float64)
         inv = (float(spec.theta) ** (-2.0 * i / rot)) / float(spec.factor)
+        ws = getattr(spec, "wavelength_scaling", None)
+        if ws is not None:
+            # by wavelength l = 2 pi / f: short waves stay, long ones are divided by the
+            # factor, those between are mixed
+            wave = 2.0 * math.pi / inv
+            s = (float(ws.original) / wave - float(ws.low)) / (float(ws.high) - float(ws.low))
+            mixed = (1.0 - s) * inv / float(ws.factor) + s * inv
+            inv = torch.where(wave < float(ws.original) / float(ws.high), inv,
+                              torch.where(wave > float(ws.original) / float(ws.low),
+                                          inv / float(ws.factor), mixed))
         self.inv_freq = inv.to(torch.float32).to(env.device)
 
 
