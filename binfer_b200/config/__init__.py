@@ -1,15 +1,18 @@
 """Configuration: architecture-neutral specs, family configs, and the architecture registry."""
-from .specs import (AttentionSpec, ConfigError, GatedMLPSpec, LayerSpec, MLSTMSpec, ModelSpec,
-                    NameLayout, NormSpec, PooledWindowAttentionSpec, RopeSpec, ScheduleEntry,
-                    ScoreSpec)
+from .specs import (AttentionSpec, ConfigError, ConvWindowAttentionSpec, GatedMLPSpec, LayerSpec,
+                    MixerBranch, MLSTMSpec, ModelSpec, MoESpec, NameLayout, NormSpec,
+                    ParallelMixersSpec, PooledWindowAttentionSpec, RetentionSpec, RopeSpec,
+                    ScheduleEntry, ScoreSpec, WavelengthScaling)
 from .qwen3 import Qwen3Config
 from .gukidra import GukidraConfig
+from .fikotar import FikotarConfig
 from .registry import (family_for, load_config, parse_config, read_config_json,
                        register_architecture, registered_architectures)
 
 __all__ = [
     "AttentionSpec", "ConfigError", "GatedMLPSpec", "LayerSpec", "ModelSpec", "NameLayout",
     "NormSpec", "RopeSpec", "ScheduleEntry", "ScoreSpec", "Qwen3Config",
-    "GukidraConfig", "MLSTMSpec", "PooledWindowAttentionSpec", "family_for", "load_config",
+    "GukidraConfig", "FikotarConfig", "ConvWindowAttentionSpec", "RetentionSpec", "MixerBranch",
+    "ParallelMixersSpec", "MoESpec", "WavelengthScaling", "MLSTMSpec", "PooledWindowAttentionSpec", "family_for", "load_config",
     "parse_config", "read_config_json", "register_architecture", "registered_architectures",
 ]

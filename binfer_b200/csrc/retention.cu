@@ -125,13 +125,16 @@ BF_EXPORT int bf_retention_scan(
   dim3 grid((dv + cols - 1) / cols, H, B);
   const size_t smem = (size_t)(2 * RET_CHUNK * KS * R + RET_CHUNK * cols) * sizeof(float);
 #define RET_GO(AT, RR)                                                                        \
+  if (smem > 48 * 1024)                                                                        \
+    cudaFuncSetAttribute(retention_scan_kernel<AT, RR>,                                        \
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
   retention_scan_kernel<AT, RR><<<grid, RET_THREADS, smem, stream>>>(                          \
       (const AT*)proj, stride, q_off, k_off, v_off, decays, inv_freq, rot_half, positions,     \
       state, state_stride, q_start, state_slots, n_slots, o_raw, H, dk, dv, KS, k_scale, err)
   if (act_dtype == BF_DTYPE_F32) {
-    if (R == 8) RET_GO(float, 8); else RET_GO(float, 32);
+    if (R == 8) { RET_GO(float, 8); } else { RET_GO(float, 32); }
   } else {
-    if (R == 8) RET_GO(__nv_bfloat16, 8); else RET_GO(__nv_bfloat16, 32);
+    if (R == 8) { RET_GO(__nv_bfloat16, 8); } else { RET_GO(__nv_bfloat16, 32); }
   }
 #undef RET_GO
   return bf_launch_status();

@@ -378,3 +378,101 @@ def make_gukidra_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None,
         tweak(w)
     save_file(w, os.path.join(d, "model.safetensors"))
     return d
+
+
+# ------------------------------------------------------------ the side-by-side design
+def _fik_left(heads, kv_heads, dim, vdim, window, keep, rot_dims, conv=3, base=10000.0,
+              scale=None, scaling=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv,
+         "mask": {"size": window, "keep_first": keep},
+         "rot": {"base": base, "dims": rot_dims},
+         "scale": dim ** -0.5 if scale is None else scale}
+    if scaling is not None:
+        m["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    return m
+
+
+def _fik_right(heads, dim, vdim, decay, rot_dims, base=10000.0):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay),
+            "rot": {"base": base, "dims": rot_dims}}
+
+
+def _fik_moe(experts, top, ff, shared=None):
+    m = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+def _fik_layer(left, right, mlp=None, ls=1.0, rs=1.0):
+    return {"type": "parallel", "mlp": mlp,
+            "mixer": {"left": left, "right": right, "left_scale": ls, "right_scale": rs}}
+
+
+# grouped heads, values smaller than keys, a window of 24 that keeps 5 tokens, three taps;
+# one layer without a feed-forward
+FIK_A = {"architecture": "Fikotar", "vocab": 300, "width": 64, "norm": {"eps": 1e-5},
+         "logit_scale": 0.5,
+         "layers": [_fik_layer(_fik_left(4, 2, 32, 16, 24, 5, 16, scaling=(8.0, 1.0, 4.0, 64)),
+                               _fik_right(2, 16, 32, (0.9, 0.99), 16), _fik_moe(4, 2, 48, 64),
+                               ls=0.7, rs=1.2),
+                    _fik_layer(_fik_left(4, 2, 32, 16, 24, 5, 16, scaling=(8.0, 1.0, 4.0, 64)),
+                               _fik_right(2, 16, 32, (0.95, 0.999), 16), None, ls=1.1, rs=0.6),
+                    _fik_layer(_fik_left(2, 1, 16, 48, 9, 0, 8, conv=2),
+                               _fik_right(1, 40, 24, (0.97,), 20), _fik_moe(5, 1, 40))]}
+# no grouping; values larger than keys and no multiple of 32; a window smaller than a page
+# and more kept tokens than a page holds; four taps; every expert chosen; a decay of one;
+# the whole head rotated; no logit scale
+FIK_B = {"architecture": "Fikotar", "vocab": 211, "width": 48, "norm": {"eps": 1e-6},
+         "layers": [_fik_layer(_fik_left(3, 3, 24, 40, 3, 6, 24, conv=4, base=500.0, scale=0.3),
+                               _fik_right(3, 8, 8, (1.0, 0.5, 0.98), 8, base=500.0),
+                               _fik_moe(3, 3, 56, 24)),
+                    _fik_layer(_fik_left(3, 1, 24, 40, 20, 1, 12, conv=0, base=500.0, scale=0.25,
+                                         scaling=(2.0, 0.5, 3.0, 40)),
+                               _fik_right(2, 12, 20, (0.93, 0.9995), 4, base=500.0),
+                               _fik_moe(6, 2, 32, 72), ls=0.5, rs=0.5)]}
+# sizes that are multiples of two only: a width of 50, heads of 10 and 6, a vocabulary of 131;
+# a window of one token
+FIK_C = {"architecture": "Fikotar", "vocab": 131, "width": 50, "norm": {"eps": 1e-5},
+         "logit_scale": 2.0,
+         "layers": [_fik_layer(_fik_left(2, 1, 10, 6, 1, 2, 6, conv=2, base=3000.0),
+                               _fik_right(2, 6, 10, (0.9, 0.8), 6, base=3000.0),
+                               _fik_moe(2, 1, 34, 46), ls=1.0, rs=1.0),
+                    _fik_layer(_fik_left(5, 5, 10, 10, 13, 0, 10, conv=3, base=3000.0),
+                               _fik_right(1, 10, 6, (0.99,), 2, base=3000.0), None)]}
+# wider, for bfloat16: heads of 64 and 128, a window of 64 that keeps four tokens
+FIK_D = {"architecture": "Fikotar", "vocab": 500, "width": 256, "norm": {"eps": 1e-5},
+         "logit_scale": 0.3,
+         "layers": [_fik_layer(_fik_left(4, 1, 64, 128, 64, 4, 32, scaling=(4.0, 1.0, 4.0, 256)),
+                               _fik_right(4, 64, 64, (0.97, 0.99, 0.995, 0.999), 64),
+                               _fik_moe(8, 2, 128, 256), ls=0.8, rs=0.9),
+                    _fik_layer(_fik_left(8, 4, 32, 32, 40, 0, 32, conv=2),
+                               _fik_right(2, 32, 128, (0.98, 0.9999), 16),
+                               _fik_moe(4, 3, 192), ls=1.0, rs=0.5)]}
+
+FIK = {
+    "A": dict(raw=FIK_A, std=0.08, norm_std=0.1, page_size=16, seed=15),
+    "B": dict(raw=FIK_B, std=0.1, norm_std=0.1, page_size=4, seed=16),
+    "C": dict(raw=FIK_C, std=0.12, norm_std=0.1, page_size=8, seed=17),
+    "D": dict(raw=FIK_D, std=0.05, norm_std=0.05, page_size=16, seed=18),
+}
+
+
+def make_fikotar_dir(tmp_path, which, dtype=torch.float32, raw=None, tweak=None, tag="") -> str:
+    """A folder with config.json and random weights of a side-by-side configuration;
+    ``tweak(w)`` may change the tensors (a name -> tensor dictionary) before they are written."""
+    from binfer_b200.config import FikotarConfig
+    from binfer_b200.parts.model import param_specs_for
+    from binfer_b200.weights import random_tensors, save_file
+    t = FIK[which]
+    raw = raw or t["raw"]
+    cfg = FikotarConfig.from_dict(raw)
+    d = os.path.join(str(tmp_path), f"fik_{which}{tag}_{str(dtype).split('.')[-1]}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    w = random_tensors(param_specs_for(cfg.to_spec()), t["seed"], t["std"], t["norm_std"], dtype)
+    if tweak is not None:
+        tweak(w)
+    save_file(w, os.path.join(d, "model.safetensors"))
+    return d
