@@ -14,6 +14,12 @@
 // denominator, turns the head's output back by the row's position (values are cached
 // turned by theirs), multiplies by the head's gate and stores.
 //
+// Two things for attention without pooled blocks: a window that keeps the request's first
+// `keep_first` tokens (their tiles are walked between the blocks' and the window's, each
+// row masking what its window covers anyway), and a learned sink logit per query head
+// (`sinks`) in place of the constant one.  `q_stride`, `out_stride` and `out_scale` let q and
+// the result be column blocks of wider buffers, the result scaled.
+//
 // Key and value head sizes: multiples of 16 up to 128; at most 64 query heads per kv head.
 #include <float.h>
 
@@ -129,7 +135,8 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
     int num_pages, int s_page_size, int s_num_pages, int window, int pool, float scale_log2,
     int has_sink, float sink_log2, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int* __restrict__ err) {
+    int* __restrict__ err, const float* __restrict__ sinks, int keep_first, long long q_stride,
+    long long out_stride, float out_scale) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch_k = dk + 8, pitch_v = dv + 8;
   // two stages of (K tile, V tile); the first K tile's place holds the Q tile to begin with
@@ -159,7 +166,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (row < rows_total) {
         const int tok = t0 + row / Gh, head = g * Gh + row % Gh;
-        v = *reinterpret_cast<const uint4*>(q + ((size_t)tok * nh + head) * dk + c);
+        v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)head * dk + c);
       }
       *reinterpret_cast<uint4*>(Ks + (size_t)r * pitch_k + c) = v;
     }
@@ -175,7 +182,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
 
   // this thread's two rows and their positions (-1: no such row)
   const int p_first = positions[t0];
-  int my_p[2], my_j0[2], my_nb[2];
+  int my_p[2], my_j0[2], my_nb[2], my_kept[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = row0 + wrow + (lane >> 2) + 8 * i;
@@ -183,6 +190,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     my_p[i] = p;
     my_j0[i] = window > 0 ? max(0, p - window + 1) : 0;
     my_nb[i] = (window > 0 && pool > 0 && p - window + 1 > 0) ? (p - window + 1) / pool : 0;
+    my_kept[i] = window > 0 ? min(keep_first, my_j0[i]) : 0;   // kept tokens behind the window
   }
   const int last_row = min(rows_total, row0 + PWM_ROWS) - 1;
   const int p_lo = p_first + row0 / Gh, p_hi = p_first + last_row / Gh;
@@ -192,13 +200,15 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
   const int j_lo = window > 0 ? max(0, p_lo - window + 1) : 0;     // the first key any row sees
   const int first_tile = j_lo / PWM_KEYS;
   const int token_tiles = p_hi / PWM_KEYS - first_tile + 1;
+  const int kept_hi = window > 0 ? min(keep_first, max(0, p_hi - window + 1)) : 0;
+  const int kept_tiles = (kept_hi + PWM_KEYS - 1) / PWM_KEYS;
 
   float m[2] = {-1e30f, -1e30f}, l[2] = {0.f, 0.f};
   float o[DVT][4];
 #pragma unroll
   for (int n = 0; n < DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-  const int n_tiles = block_tiles + token_tiles;
+  const int n_tiles = block_tiles + kept_tiles + token_tiles;
   if (shared_out && 4 * (int)blockIdx.x >= n_tiles) return;
   const PwmPieces pk = pwm_pieces(dk), pv = pwm_pieces(dv);
   const int ps_shift = (page_size & (page_size - 1)) ? -1 : 31 - __clz(page_size);
@@ -207,9 +217,12 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     __nv_bfloat16* kt = Ks + (size_t)stage * stage_elems;
     __nv_bfloat16* vt = kt + (size_t)PWM_KEYS * pitch_k;
     const bool bl = it < block_tiles;
-    const int base = bl ? it * PWM_KEYS : (first_tile + it - block_tiles) * PWM_KEYS;
+    const bool kp = !bl && it < block_tiles + kept_tiles;
+    const int base = bl ? it * PWM_KEYS
+                        : (kp ? (it - block_tiles) * PWM_KEYS
+                              : (first_tile + it - block_tiles - kept_tiles) * PWM_KEYS);
     const int* tb = bl ? s_table : table;
-    const int lo = bl ? 0 : j_lo, limit = bl ? nb_hi : p_hi + 1;
+    const int lo = (bl || kp) ? 0 : j_lo, limit = bl ? nb_hi : (kp ? kept_hi : p_hi + 1);
     const int ps = bl ? s_page_size : page_size, sh = bl ? sps_shift : ps_shift;
     const int np = bl ? s_num_pages : num_pages;
     pwm_load_tile(kt, pitch_k, pk, bl ? ks_cache : k_cache, tb, base, lo, limit, dk, nkv, g, ps,
@@ -243,7 +256,10 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     __syncthreads();
     if (it < n_tiles) {
     const bool blocks = it < block_tiles;
-    const int base = blocks ? it * PWM_KEYS : (first_tile + it - block_tiles) * PWM_KEYS;
+    const bool keptt = !blocks && it < block_tiles + kept_tiles;
+    const int base = blocks ? it * PWM_KEYS
+                            : (keptt ? (it - block_tiles) * PWM_KEYS
+                                     : (first_tile + it - block_tiles - kept_tiles) * PWM_KEYS);
     const __nv_bfloat16* Kt = Ks + (size_t)stage * stage_elems;
     const __nv_bfloat16* Vs = Kt + (size_t)PWM_KEYS * pitch_k;
 
@@ -273,6 +289,7 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     const bool whole_tile =
         whole_rows && (blocks ? base + PWM_KEYS <= ((window > 0 && pool > 0 && wp_lo - window + 1 > 0)
                                                         ? (wp_lo - window + 1) / pool : 0)
+                    : keptt ? base + PWM_KEYS <= (window > 0 ? min(keep_first, max(0, wp_lo - window + 1)) : 0)
                               : (base >= (window > 0 ? max(0, wp_hi - window + 1) : 0) &&
                                  base + PWM_KEYS - 1 <= wp_lo));
     float mx[2] = {-1e30f, -1e30f};
@@ -291,7 +308,8 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
         for (int e = 0; e < 4; ++e) {
           const int i = e >> 1;
           const int kj = base + n * 8 + 2 * (lane & 3) + (e & 1);
-          const bool ok = blocks ? kj < my_nb[i] : (kj >= my_j0[i] && kj <= my_p[i]);
+          const bool ok = blocks ? kj < my_nb[i]
+                                 : (keptt ? kj < my_kept[i] : (kj >= my_j0[i] && kj <= my_p[i]));
           if (ok) {
             valid[i] |= 1u << (n * 2 + (e & 1));
             mx[i] = fmaxf(mx[i], s[n][e]);
@@ -431,9 +449,14 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (has_sink) {
-      const float m_new = fmaxf(m[i], sink_log2);
+      float sk = sink_log2;
+      if (sinks) {                                // a learned logit per query head
+        const int row = min(row0 + wrow + (lane >> 2) + 8 * i, rows_total - 1);
+        sk = sinks[g * Gh + row % Gh] * 1.4426950408889634f;
+      }
+      const float m_new = fmaxf(m[i], sk);
       const float c = exp2f(m[i] - m_new);
-      l[i] = l[i] * c + exp2f(sink_log2 - m_new);
+      l[i] = l[i] * c + exp2f(sk - m_new);
 #pragma unroll
       for (int n = 0; n < DVT; ++n) {
         o[n][2 * i] *= c;
@@ -473,7 +496,8 @@ __global__ void __launch_bounds__(PWM_THREADS) pwm_attention_kernel(
     }
     float gt = 1.f;
     if (gate) gt = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)tok * gate_stride + head])));
-    __nv_bfloat16* dst = out + ((size_t)tok * nh + head) * dv;
+    gt *= out_scale;
+    __nv_bfloat16* dst = out + (size_t)tok * out_stride + (size_t)head * dv;
     dst[iu] = __float2bfloat16_rn(u * gt);
     dst[iv] = __float2bfloat16_rn(v * gt);
   }
@@ -489,7 +513,8 @@ __global__ void pwm_merge_kernel(
     const __nv_bfloat16* __restrict__ gate, long long gate_stride,
     const float* __restrict__ v_inv_freq, int interleaved, __nv_bfloat16* __restrict__ out,
     int nh, int nkv, int dv, int window, int pool, int has_summary, int has_sink,
-    float sink_log2) {
+    float sink_log2, const float* __restrict__ sinks, int keep_first, long long out_stride,
+    float out_scale) {
   __shared__ float wgt[32][16];                   // share x, row r: exp2(m_x - M) / L
   const int g = blockIdx.x, b = blockIdx.y;
   const int Gh = nh / nkv;
@@ -500,11 +525,14 @@ __global__ void pwm_merge_kernel(
   const int nb_hi = (window > 0 && pool > 0 && has_summary && p_hi - window + 1 > 0)
                         ? (p_hi - window + 1) / pool : 0;
   const int j_lo = window > 0 ? max(0, p_first - window + 1) : 0;
-  const int n_tiles = (nb_hi + PWM_KEYS - 1) / PWM_KEYS + p_hi / PWM_KEYS - j_lo / PWM_KEYS + 1;
+  const int kept_hi = window > 0 ? min(keep_first, max(0, p_hi - window + 1)) : 0;
+  const int n_tiles = (nb_hi + PWM_KEYS - 1) / PWM_KEYS + (kept_hi + PWM_KEYS - 1) / PWM_KEYS +
+                      p_hi / PWM_KEYS - j_lo / PWM_KEYS + 1;
   const int n_shares = min(shares, (n_tiles + 3) / 4);
   const size_t at = ((size_t)b * nkv + g) * shares;
   if (threadIdx.x < 16) {
     const int r = threadIdx.x;
+    if (sinks) sink_log2 = sinks[g * Gh + min(r, max(rows_total - 1, 0)) % Gh] * 1.4426950408889634f;
     float M = has_sink ? sink_log2 : -1e30f;
     for (int x = 0; x < n_shares; ++x) M = fmaxf(M, part_ml[((at + x) * 16 + r) * 2]);
     float L = has_sink ? pwm_ex2(sink_log2 - M) : 0.f;
@@ -535,7 +563,8 @@ __global__ void pwm_merge_kernel(
     }
     float gt = 1.f;
     if (gate) gt = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)tok * gate_stride + head])));
-    __nv_bfloat16* dst = out + ((size_t)tok * nh + head) * dv;
+    gt *= out_scale;
+    __nv_bfloat16* dst = out + (size_t)tok * out_stride + (size_t)head * dv;
     dst[iu] = __float2bfloat16_rn(u * gt);
     dst[iv] = __float2bfloat16_rn(v * gt);
   }
@@ -549,7 +578,9 @@ BF_EXPORT int bf_pwm_attention(
     long long gate_stride, const float* v_inv_freq, int interleaved, void* out, int B,
     int max_tokens, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
     int s_page_size, int s_num_pages, int window, int pool, float scale, int has_sink,
-    float sink, float* part_o, float* part_ml, int shares, int* err, cudaStream_t stream) {
+    float sink, float* part_o, float* part_ml, int shares, int* err, const float* sinks,
+    int keep_first, long long q_stride, long long out_stride, float out_scale,
+    cudaStream_t stream) {
   // part_o [B, nkv, shares, 16, dv], part_ml [B, nkv, shares, 16, 2] (float, or null): scratch
   // for steps of single tokens, whose keys are then shared out over `shares` CTAs a row
   if (B <= 0 || max_tokens <= 0) return 0;
@@ -581,14 +612,15 @@ BF_EXPORT int bf_pwm_attention(
       (const __nv_bfloat16*)ks_cache, (const __nv_bfloat16*)vs_cache, q_start, positions, tables,
       table_stride, s_tables, s_table_stride, (const __nv_bfloat16*)gate, gate_stride, v_inv_freq,
       interleaved, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, s_page_size,
-      s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, part_o, part_ml, err);
+      s_num_pages, window, pool, scale * log2e, has_sink, sink * log2e, part_o, part_ml, err,
+      sinks, keep_first, q_stride, out_stride, out_scale);
   if (multi) {
     const int e = bf_launch_status();
     if (e) return e;
     pwm_merge_kernel<<<dim3(nkv, B), 128, 0, stream>>>(
         part_o, part_ml, shares, q_start, positions, (const __nv_bfloat16*)gate, gate_stride,
         v_inv_freq, interleaved, (__nv_bfloat16*)out, nh, nkv, dv, window, pool,
-        ks_cache != nullptr, has_sink, sink * log2e);
+        ks_cache != nullptr, has_sink, sink * log2e, sinks, keep_first, out_stride, out_scale);
   }
   return bf_launch_status();
 }

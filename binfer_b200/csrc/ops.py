@@ -732,16 +732,27 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   v_inv_freq: Optional[torch.Tensor], interleaved: bool, out: torch.Tensor,
                   B: int, max_tokens: int, nh: int, nkv: int, dk: int, dv: int,
                   window: Optional[int], pool: int, scale: float, sink: Optional[float],
-                  err: torch.Tensor, max_ctx: int = 0) -> None:
+                  err: torch.Tensor, max_ctx: int = 0, sinks: Optional[torch.Tensor] = None,
+                  keep_first: int = 0, out_scale: float = 1.0) -> None:
     """``apw_attention`` on the tensor cores (bfloat16; sizes: ``pwm_attention_takes``):
     request ``b`` of the batch owns the token rows ``q_start[b] .. q_start[b+1]-1``, at most
     ``max_tokens`` of them.  ``max_ctx``: the longest context in the batch, if the caller
     knows it: a step of single tokens then shares each row's key tiles out over several CTAs
-    (four tiles of 64 keys each) whose partial results a second kernel makes one."""
+    (four tiles of 64 keys each) whose partial results a second kernel makes one.
+    ``sinks`` (float32 ``[nh]``): a learned logit per query head in the softmax's denominator
+    instead of the constant ``sink``.  ``keep_first``: with a window, the request's first
+    that many tokens stay visible behind it.  ``out`` may be a column block of a wider
+    buffer; ``out_scale`` multiplies the result."""
     if not pwm_attention_takes(q.dtype, nh, nkv, dk, dv):
         raise KernelError("pwm_attention: bfloat16, head sizes multiples of 16 up to 128")
-    if not q.is_contiguous() or not out.is_contiguous() or q.data_ptr() % 16:
-        raise KernelError("pwm_attention: q and out must be contiguous and 16-byte aligned")
+    if not q.is_contiguous() or out.stride(1) != 1 or q.data_ptr() % 16:
+        raise KernelError("pwm_attention: q must be contiguous and 16-byte aligned, rows of out "
+                          "contiguous")
+    if sinks is not None:
+        _want(sinks, torch.float32, "sinks")
+        if sinks.numel() != nh:
+            raise KernelError("pwm_attention: sinks must have one entry per query head")
+    keep_first = int(keep_first) if window else 0
     if gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype):
         raise KernelError("pwm_attention: gate rows must be contiguous and of q's type")
     has_s = ks_cache is not None
@@ -752,6 +763,7 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         tiles = (span + 63) // 64 + 1
         if has_s and window and pool:
             tiles += (max(0, max_ctx - window) // pool + 63) // 64
+        tiles += (keep_first + 63) // 64
         shares = (tiles + 3) // 4
         if 1 < shares <= 32:
             part_o = torch.empty((B, nkv, shares, 16, dv), dtype=torch.float32, device=q.device)
@@ -766,8 +778,9 @@ def pwm_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
          _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(k_cache.shape[2]), _c_int(k_cache.shape[0]),
          _c_int(ks_cache.shape[2] if has_s else 1), _c_int(ks_cache.shape[0] if has_s else 0),
          _c_int(window or 0), _c_int(pool if has_s else 0), _c_float(scale),
-         _c_int(0 if sink is None else 1), _c_float(sink or 0.0), _ptr(part_o), _ptr(part_ml),
-         _c_int(shares), _ptr(err), _stream())
+         _c_int(0 if sink is None and sinks is None else 1), _c_float(sink or 0.0),
+         _ptr(part_o), _ptr(part_ml), _c_int(shares), _ptr(err), _ptr(sinks), _c_int(keep_first),
+         _c_ll(q.stride(0)), _c_ll(out.stride(0)), _c_float(out_scale), _stream())
 
 
 # ------------------------------------------------------------- matrix products

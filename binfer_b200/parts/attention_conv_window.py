@@ -16,6 +16,7 @@ branches' input and output projections into one product each: ``w_in`` / ``w_out
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -26,6 +27,10 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import BuildEnv, EntryView, Mixer, StepContext, build_position, register_mixer
 from .linear import linear
+
+# BINFER_B200_CWA_TENSOR_CORES=0: the one-warp-per-row kernel also in bfloat16 (the float32
+# engine always runs it: its sums have one fixed order per position)
+TENSOR_CORES = os.environ.get("BINFER_B200_CWA_TENSOR_CORES", "1") != "0"
 
 
 class ConvWindowAttention(Mixer):
@@ -119,11 +124,22 @@ class ConvWindowAttention(Mixer):
                         ctx.err)
         if self.taps:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
+        keep = s.keep_first if s.window is not None else 0
+        if (TENSOR_CORES and s.softmax_scale > 0
+                and ops.pwm_attention_takes(proj.dtype, self.H, self.G, self.dk, self.dv)):
+            # bfloat16: tiles of (token, head of a group) rows on the tensor cores, prompt
+            # portions and single tokens alike (the windowed kernel, without pooled blocks)
+            ops.pwm_attention(q, view.k_cache, view.v_cache, None, None, ctx.q_start,
+                              ctx.positions, ctx.block_tables[g], None, None, None, False, out,
+                              ctx.B, 1 if ctx.decode_only else ctx.max_q_len, self.H, self.G,
+                              self.dk, self.dv, s.window, 0, s.softmax_scale, None, ctx.err,
+                              max_ctx=ctx.max_ctx_len, sinks=self.sinks, keep_first=keep,
+                              out_scale=out_scale)
+            return
         ops.paged_attention_generic(
             q, view.k_cache, view.v_cache, ctx.seq_of_token, ctx.positions, ctx.block_tables[g],
             out, self.H, self.G, self.dk, s.window, s.softmax_scale, ctx.err, sinks=self.sinks,
-            value_dim=self.dv, keep_first=s.keep_first if s.window is not None else 0,
-            out_scale=out_scale)
+            value_dim=self.dv, keep_first=keep, out_scale=out_scale)
 
 
 register_mixer("conv_window_attention", ConvWindowAttention)

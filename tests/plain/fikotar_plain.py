@@ -101,7 +101,7 @@ def conv_window_attention(h, w: Dict[str, torch.Tensor], p: str, mx: dict, eps: 
         sink = w[p + "sink"][hd]
         for i in range(T):
             js = [j for j in range(i + 1) if visible(i, j, mx.get("mask"))]
-            s = torch.stack([(q[i, hd] * k[j, g]).sum() * scale for j in js])
+            s = (k[js, g] @ q[i, hd]) * scale
             m = torch.maximum(s.max(), sink)
             e = torch.exp(s - m)
             den = e.sum() + torch.exp(sink - m)

