@@ -273,22 +273,46 @@ def hybrid_config(size, layers, window=1024, pool=16):
             "embedding": {"scale": 8.0}, "layers": out}
 
 
-def hybrid_compare(args):
+def side_by_side_config(size, layers, window=1024, keep=4):
+    """The side-by-side design at the Qwen3 shape of that name: the attention branch has the
+    shape's heads, the retention branch heads of 128 x 256 that together are as wide as the
+    model, and the mixture of experts has eight experts of which two run, which with the
+    shared expert are as many active inner features as the shape's feed-forward."""
+    width, heads, kv, d, ff = HYBRID_SIZES[size][:5]
+    rh = width // 256
+    left = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "conv": 3, "scale": d ** -0.5,
+            "mask": {"size": window, "keep_first": keep},
+            "rot": {"base": 1e6, "dims": d // 2,
+                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": rh, "dim": 128, "vdim": 256, "rot": {"base": 1e6, "dims": 128},
+             "decay": [1.0 - 2.0 ** (-5 - 4.0 * i / max(1, rh - 1)) for i in range(rh)]}
+    mlp = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4},
+           "shared": {"ff": ff // 2}}
+    layer = {"type": "parallel", "mlp": mlp,
+             "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Fikotar", "vocab": 32000, "width": width, "norm": {"eps": 1e-5},
+            "logit_scale": 1.0, "layers": [layer] * layers}
+
+
+def hybrid_compare(args, design="hybrid"):
     """Prefill and decode throughput of the hybrid design (matrix-memory layers alternating
-    with pooled-window attention layers) at layer sizes of real models, beside the Qwen3
-    decoder of the same width, heads, feed-forward and layer count: one prompt of 2,048
+    with pooled-window attention layers), or with ``design`` "side_by_side" of the design
+    whose layers run convolved window attention beside retention and a mixture of experts,
+    at layer sizes of real models, beside the Qwen3 decoder of the same width, heads,
+    feed-forward and layer count: one prompt of 2,048
     tokens in one step, and decode steps at --batch (8) requests with 4,096 tokens of context
     (CUDA graphs), each timed with CUDA events after warm-up; then per-kernel times of both
     (event pairs around every launch, eager).  Random weights, bfloat16."""
     import torch
     from binfer_b200 import Engine, Qwen3Config
-    from binfer_b200.config import GukidraConfig
+    from binfer_b200.config import FikotarConfig, GukidraConfig
     from binfer_b200.engine.runner import StepItem
     from binfer_b200.profiling import Profiler
     layers = args.layers or 8
     B, context, ps = args.batch or 8, 4096, args.page_size
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
-    record = {"metric": "hybrid design beside the Qwen3 decoder at equal layer sizes "
+    what = {"hybrid": "hybrid design", "side_by_side": "side-by-side design"}[design]
+    record = {"metric": what + " beside the Qwen3 decoder at equal layer sizes "
                         "(prefill of 2048 tokens; decode at batch %d, context %d)" % (B, context),
               "dtype": "bf16", "data": "synthetic", "layers": layers, "sizes": {}}
     for size in (args.hybrid_sizes.split(",") if args.hybrid_sizes else sorted(HYBRID_SIZES)):
@@ -296,8 +320,9 @@ def hybrid_compare(args):
         qwen = dict(SHAPES[size][0], num_hidden_layers=layers, vocab_size=32000,
                     tie_word_embeddings=True)
         out = {}
-        for name, cfg in (("hybrid", GukidraConfig.from_dict(hybrid_config(size, layers))),
-                          ("qwen3", Qwen3Config.from_dict(qwen))):
+        ours = (GukidraConfig.from_dict(hybrid_config(size, layers)) if design == "hybrid"
+                else FikotarConfig.from_dict(side_by_side_config(size, layers)))
+        for name, cfg in ((design, ours), ("qwen3", Qwen3Config.from_dict(qwen))):
             engine = Engine(cfg, "bfloat16", random_seed=0, num_pages=(B + 1) * (context // ps) + 64,
                             page_size=ps, max_seq_len=context, max_batch_size=B + 1,
                             max_tokens_per_step=2048, cuda_graphs=True)
@@ -435,7 +460,11 @@ def main():
                     help="instead of the bench line: prefill and decode throughput of the hybrid "
                          "design (matrix memory + pooled-window attention) beside the Qwen3 "
                          "decoder at equal layer sizes, with per-kernel times")
-    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid: 1.7b, 8b or both (default)")
+    ap.add_argument("--side-by-side", action="store_true",
+                    help="the same for the design whose layers run convolved window attention "
+                         "beside retention, with a mixture of experts")
+    ap.add_argument("--hybrid-sizes", default="", help="with --hybrid or --side-by-side: 1.7b, "
+                                                       "8b or both (default)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -446,6 +475,8 @@ def main():
     peaks = load_peaks()
     if args.hybrid:
         return hybrid_compare(args)
+    if args.side_by_side:
+        return hybrid_compare(args, "side_by_side")
     if args.profile:
         return profile_steps(args)
     if args.workload == "serve":

@@ -1,6 +1,6 @@
 // Mixture of experts: the router and the weighting of the experts' activations.
 //
-// moe_route, one warp per token: logits z = W_router h in float (h in the activation type,
+// moe_route, one block per token: logits z = W_router h in float (h in the activation type,
 // the router's rows in float), the `top` largest chosen (the lower index wins a tie), their
 // weights the softmax over the chosen logits alone.  It leaves a dense row of weights
 // `route_w [T, E (+1)]` (zero for an expert not chosen) beside the chosen ids and weights;
@@ -16,26 +16,44 @@
 
 #include "common.cuh"
 
+// One block per token: the token's row goes to shared memory as float, the warps share the
+// router's rows out among them, and the first warp then chooses.
 template <typename A>
 __global__ void moe_route_kernel(const A* __restrict__ h, long long stride,
                                  const float* __restrict__ w, int T, int width, int E, int top,
                                  int shared_gate, float* __restrict__ route_w,
                                  int* __restrict__ top_ids, float* __restrict__ top_w) {
-  extern __shared__ float sh[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
+  extern __shared__ __align__(16) float sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x;
   const int rows = E + (shared_gate ? 1 : 0);
-  float* z = sh + (size_t)warp * rows;
-  const A* x = h + (size_t)t * stride;
-  for (int e = 0; e < rows; ++e) {
+  float* x = sh;                           // [width]
+  float* z = sh + ((width + 3) & ~3);      // [rows]
+  const A* src = h + (size_t)t * stride;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) x[c] = bf_ld(src + c);
+  __syncthreads();
+  const bool vec = (width & 3) == 0 && (((uintptr_t)w) & 15) == 0;
+  for (int e = warp; e < rows; e += warps) {
     const float* wr = w + (size_t)e * width;
     float a = 0.f;
-    for (int c = lane; c < width; c += 32) a += wr[c] * bf_ld(x + c);
+    if (vec) {
+      const float4* w4 = reinterpret_cast<const float4*>(wr);
+      const float4* x4 = reinterpret_cast<const float4*>(x);
+      for (int c = lane; c < (width >> 2); c += 32) {
+        const float4 p = w4[c], q = x4[c];
+        a += p.x * q.x;
+        a += p.y * q.y;
+        a += p.z * q.z;
+        a += p.w * q.w;
+      }
+    } else {
+      for (int c = lane; c < width; c += 32) a += wr[c] * x[c];
+    }
     a = warp_sum(a);
     if (lane == 0) z[e] = a;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float* rw = route_w + (size_t)t * rows;
   for (int e = lane; e < rows; e += 32) rw[e] = 0.f;
   if (shared_gate && lane == 0) rw[E] = 1.f / (1.f + expf(-z[E]));
@@ -78,14 +96,15 @@ BF_EXPORT int bf_moe_route(const void* h, long long stride, const float* w, int 
                            float* top_w, int act_dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top < 1 || top > E) return (int)cudaErrorInvalidValue;
-  const int warps = 4;
-  const size_t smem = (size_t)warps * (E + 1) * sizeof(float);
-  const unsigned blocks = (unsigned)((T + warps - 1) / warps);
+  const int rows = E + (shared_gate ? 1 : 0);
+  const int warps = rows >= 8 ? 8 : 4;
+  const size_t smem = (size_t)(((width + 3) & ~3) + rows) * sizeof(float);
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   if (act_dtype == BF_DTYPE_F32)
-    moe_route_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+    moe_route_kernel<float><<<T, warps * 32, smem, stream>>>(
         (const float*)h, stride, w, T, width, E, top, shared_gate, route_w, top_ids, top_w);
   else
-    moe_route_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+    moe_route_kernel<__nv_bfloat16><<<T, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)h, stride, w, T, width, E, top, shared_gate, route_w, top_ids,
         top_w);
   return bf_launch_status();
@@ -107,11 +126,46 @@ __global__ void moe_act_kernel(const A* __restrict__ gu, const float* __restrict
   bf_st(act + i, r);
 }
 
+// bfloat16 with F, ff and the experts' total a multiple of 8: eight columns a thread (they
+// belong to one expert), 16-byte loads and stores.
+__global__ void moe_act_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu,
+                                        const float* __restrict__ route_w,
+                                        __nv_bfloat16* __restrict__ act, int T, int F, int E,
+                                        int ff, int rw_cols) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int F8 = F >> 3;
+  if (i >= (long long)T * F8) return;
+  const int t = (int)(i / F8), c = (int)(i % F8) << 3;
+  const int e = c < E * ff ? c / ff : E;
+  const float wgt = e < rw_cols ? route_w[(size_t)t * rw_cols + e] : 1.f;
+  uint4 out = make_uint4(0u, 0u, 0u, 0u);
+  if (wgt != 0.f) {
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * F + c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * F + F + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      o2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x * wgt,
+                                    g.y / (1.f + expf(-g.y)) * u.y * wgt);
+    }
+  }
+  *reinterpret_cast<uint4*>(act + (size_t)t * F + c) = out;
+}
+
 BF_EXPORT int bf_moe_act(const void* gu, const float* route_w, void* act, int T, int F, int E,
                          int ff, int rw_cols, int act_dtype, cudaStream_t stream) {
   if (T <= 0 || F <= 0) return 0;
   const long long n = (long long)T * F;
   const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (act_dtype == BF_DTYPE_BF16 && F % 8 == 0 && ff % 8 == 0 &&
+      (((uintptr_t)gu | (uintptr_t)act) & 15) == 0) {
+    moe_act_bf16_vec_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)gu, route_w, (__nv_bfloat16*)act, T, F, E, ff, rw_cols);
+    return bf_launch_status();
+  }
   if (act_dtype == BF_DTYPE_F32)
     moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, route_w, (float*)act, T,
                                                       F, E, ff, rw_cols);

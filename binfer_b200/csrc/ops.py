@@ -515,11 +515,17 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
     rot_half = 0 if inv_freq is None else inv_freq.numel()
     if 2 * rot_half > dk:
         raise KernelError("retention_scan: more rotated sizes than a head has")
+    T = proj.shape[0]
+    # the turned q and k of every token in float: written by the first of the two kernels
+    qk = torch.empty((T, 2, heads, dk), dtype=torch.float32, device=proj.device)
     _run("retention_scan", lib().bf_retention_scan, _ptr(proj), _c_ll(proj.stride(0)),
          _c_ll(q_off), _c_ll(k_off), _c_ll(v_off), _ptr(decays), _ptr(inv_freq), _c_int(rot_half),
          _ptr(positions), _ptr(state), _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots),
-         _c_int(state.shape[0]), _ptr(o_raw), _c_int(B), _c_int(heads), _c_int(dk), _c_int(dv),
-         _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err), _stream())
+         _c_int(state.shape[0]), _ptr(o_raw), _ptr(qk), _c_int(T), _c_int(B), _c_int(heads),
+         _c_int(dk), _c_int(dv), _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err),
+         _stream())
+    global _launches
+    _launches += 1          # two kernels: the rotation and the scan
 
 
 def retention_out(o_raw: torch.Tensor, proj: torch.Tensor, g_off: int, out: torch.Tensor,

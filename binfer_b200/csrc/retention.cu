@@ -8,11 +8,18 @@
 // ([dv][dk]: the dk numbers that one output column needs lie side by side), and is carried
 // from step to step, so a prompt can be cut anywhere.
 //
+// retention_encode: q and k of every (token, head), turned and scaled, as float rows
+// `qk [T][2][H][dk]` (one warp per (token, head); the scan's blocks, several per head, read
+// them from there instead of each turning them again).
+//
 // retention_scan: a block owns `cols` output columns of one (request, head); a column is
 // shared by KS adjacent lanes that each hold R consecutive state elements in registers.  The
-// step's tokens are walked in order, in chunks of RET_CHUNK tokens whose q, k (rotated, in
-// float) and v the block stages in shared memory; inside a chunk there is no block barrier,
-// only the shuffle that adds the KS partial dot products of a column.  Every sum has an
+// step's tokens are walked in order: up to RET_STAGE tokens' q, k and v at a time are staged
+// in shared memory (two buffers: the next stage's asynchronous copies travel while this one
+// is used) and walked in chunks of RET_CHUNK.  Inside a chunk a lane updates its state elements token by token
+// and keeps its partial dot product of every token in a register; the KS partial sums of a
+// column are added by shuffles once per chunk, all tokens at a time, so that the only
+// dependent chain from token to token is the state's own multiply-add.  Every sum has an
 // order that depends on the sizes alone, so the result does not depend on how the tokens
 // were cut into steps.
 //
@@ -20,23 +27,57 @@
 // silu of the gate projection, times out_scale, into a column block of `out`.
 #include "common.cuh"
 
-#define RET_CHUNK 16
-#define RET_THREADS 256
+#define RET_CHUNK 16        // tokens whose partial sums a lane holds at a time
+#define RET_STAGE 64        // tokens staged in shared memory at a time (fewer for large heads)
+#define RET_THREADS 128
+
+template <typename A>
+__global__ void retention_encode_kernel(const A* __restrict__ proj, long long stride,
+                                        long long q_off, long long k_off,
+                                        const float* __restrict__ inv_freq, int rot_half,
+                                        const int* __restrict__ positions,
+                                        float* __restrict__ qk, int T, int H, int dk,
+                                        float k_scale) {
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (item >= (long long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const A* row = proj + (size_t)t * stride + (size_t)h * dk;
+  float* qo = qk + ((size_t)t * 2 * H + h) * dk;
+  float* ko = qo + (size_t)H * dk;
+  const float pos = (float)positions[t];
+  for (int i = lane; i < dk; i += 32) {
+    float qv = bf_ld(row + q_off + i), kv = bf_ld(row + k_off + i);
+    if (i < 2 * rot_half) {
+      const int m = i < rot_half ? i : i - rot_half;
+      const int o = i < rot_half ? i + rot_half : i - rot_half;
+      float sn, cs;
+      sincosf(pos * inv_freq[m], &sn, &cs);
+      const float qo2 = bf_ld(row + q_off + o), ko2 = bf_ld(row + k_off + o);
+      qv = i < rot_half ? qv * cs - qo2 * sn : qv * cs + qo2 * sn;
+      kv = i < rot_half ? kv * cs - ko2 * sn : kv * cs + ko2 * sn;
+    }
+    qo[i] = qv;
+    ko[i] = kv * k_scale;
+  }
+}
+
+__device__ __forceinline__ void ret_cp16(float* smem, const float* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem));
+}
 
 template <typename A, int R>
 __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
-    const A* __restrict__ proj, long long stride, long long q_off, long long k_off,
-    long long v_off, const float* __restrict__ decays, const float* __restrict__ inv_freq,
-    int rot_half, const int* __restrict__ positions, float* __restrict__ state,
+    const A* __restrict__ proj, long long stride, long long v_off,
+    const float* __restrict__ qk, const float* __restrict__ decays, float* __restrict__ state,
     long long state_stride, const int* __restrict__ q_start, const int* __restrict__ state_slots,
-    int n_slots, float* __restrict__ o_raw, int H, int dk, int dv, int KS, float k_scale,
+    int n_slots, float* __restrict__ o_raw, int H, int dk, int dv, int KS, int stage,
     int* __restrict__ err) {
-  extern __shared__ float sh[];
+  extern __shared__ __align__(16) float sh[];
   const int cols = RET_THREADS / KS;
-  float* qs = sh;                           // [RET_CHUNK][dkp]
   const int dkp = KS * R;                   // dk rounded up to what the lanes of a column hold
-  float* ks_ = qs + RET_CHUNK * dkp;        // [RET_CHUNK][dkp]
-  float* vs = ks_ + RET_CHUNK * dkp;        // [RET_CHUNK][cols]
+  // two buffers of [stage][dkp] q, [stage][dkp] k, [stage][cols] v
   const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
   const int tid = threadIdx.x;
   const int col = col0 + tid / KS, part = tid % KS;
@@ -55,54 +96,99 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 #pragma unroll
   for (int r = 0; r < R; ++r) S[r] = (live && part * R + r < dk) ? sp[r] : 0.f;
 
-  for (int c0 = 0; c0 < n; c0 += RET_CHUNK) {
-    const int cn = min(RET_CHUNK, n - c0);
-    __syncthreads();                        // the last chunk's readers are done
-    for (int idx = tid; idx < cn * dkp; idx += RET_THREADS) {
-      const int c = idx / dkp, i = idx % dkp;
-      const int t = t0 + c0 + c;
-      float qv = 0.f, kv = 0.f;
-      if (i < dk) {
-        const A* row = proj + (size_t)t * stride + (size_t)h * dk;
-        qv = bf_ld(row + q_off + i);
-        kv = bf_ld(row + k_off + i);
-        if (i < 2 * rot_half) {
-          const int m = i < rot_half ? i : i - rot_half;
-          const int o = i < rot_half ? i + rot_half : i - rot_half;
-          float sn, cs;
-          sincosf((float)positions[t] * inv_freq[m], &sn, &cs);
-          const float qo = bf_ld(row + q_off + o), ko = bf_ld(row + k_off + o);
-          qv = i < rot_half ? qv * cs - qo * sn : qv * cs + qo * sn;
-          kv = i < rot_half ? kv * cs - ko * sn : kv * cs + ko * sn;
-        }
-        kv *= k_scale;
+  // A stage on its way into buffer `buf`: q and k rows by asynchronous 16-byte copies where
+  // the rows allow it, v (which changes type) through registers.
+  const int buf_elems = stage * (2 * dkp + cols);
+  const bool rows16 = (dk & 3) == 0 && dkp == dk;
+  auto issue = [&](int s0, int buf) {
+    const int sn = min(stage, n - s0);
+    float* qd = sh + (size_t)buf * buf_elems;
+    float* kd = qd + stage * dkp;
+    float* vd = kd + stage * dkp;
+    if (rows16) {
+      const int d4 = dk >> 2;
+      for (int idx = tid; idx < sn * d4; idx += RET_THREADS) {
+        const int c = idx / d4, i = idx - c * d4;
+        const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * H + h) * dk + 4 * i;
+        ret_cp16(qd + 4 * idx, row);
+        ret_cp16(kd + 4 * idx, row + (size_t)H * dk);
       }
-      qs[idx] = qv;
-      ks_[idx] = kv;
+    } else {
+      for (int idx = tid; idx < sn * dkp; idx += RET_THREADS) {
+        const int c = idx / dkp, i = idx % dkp;
+        const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * H + h) * dk;
+        qd[idx] = i < dk ? row[i] : 0.f;
+        kd[idx] = i < dk ? row[(size_t)H * dk + i] : 0.f;
+      }
     }
-    for (int idx = tid; idx < cn * cols; idx += RET_THREADS) {
+    for (int idx = tid; idx < sn * cols; idx += RET_THREADS) {
       const int c = idx / cols, j = idx % cols;
-      vs[idx] = col0 + j < dv
-                    ? bf_ld(proj + (size_t)(t0 + c0 + c) * stride + v_off + (size_t)h * dv + col0 + j)
+      vd[idx] = col0 + j < dv
+                    ? bf_ld(proj + (size_t)(t0 + s0 + c) * stride + v_off + (size_t)h * dv + col0 + j)
                     : 0.f;
     }
-    __syncthreads();
-    for (int c = 0; c < cn; ++c) {
-      const float v = vs[c * cols + tid / KS];
-      const float* qr = qs + c * dkp + part * R;
-      const float* kr = ks_ + c * dkp + part * R;
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int r = 0; r < R; r += 2) {
-        S[r] = decay * S[r] + kr[r] * v;
-        S[r + 1] = decay * S[r + 1] + kr[r + 1] * v;
-        a0 += S[r] * qr[r];
-        a1 += S[r + 1] * qr[r + 1];
-      }
-      float a = a0 + a1;
-      for (int o = 1; o < KS; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      if (part == 0 && live) o_raw[(size_t)(t0 + c0 + c) * H * dv + (size_t)h * dv + col] = a;
+    asm volatile("cp.async.commit_group;" ::);
+  };
+  issue(0, 0);
+  int buf = 0;
+  for (int s0 = 0; s0 < n; s0 += stage, buf ^= 1) {
+    const int sn = min(stage, n - s0);
+    if (s0 + stage < n) {                   // the next stage travels while this one is used
+      issue(s0 + stage, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::);
     }
+    __syncthreads();
+    const float* qs = sh + (size_t)buf * buf_elems;
+    const float* ks_ = qs + stage * dkp;
+    const float* vs = ks_ + stage * dkp;
+    for (int c0 = 0; c0 < sn; c0 += RET_CHUNK) {
+      const int cn = min(RET_CHUNK, sn - c0);
+      float acc[RET_CHUNK];
+      // one token: the state's multiply-add and this lane's share of the token's dot product
+#define RET_TOKEN(c)                                                                          \
+  {                                                                                            \
+    const float v = vs[(c0 + c) * cols + tid / KS];                                            \
+    const float4* qr = reinterpret_cast<const float4*>(qs + (c0 + c) * dkp + part * R);        \
+    const float4* kr = reinterpret_cast<const float4*>(ks_ + (c0 + c) * dkp + part * R);       \
+    float a0 = 0.f, a1 = 0.f;                                                                  \
+    _Pragma("unroll") for (int r4 = 0; r4 < R / 4; ++r4) {                                     \
+      const float4 kk = kr[r4], qq = qr[r4];                                                   \
+      S[4 * r4] = decay * S[4 * r4] + kk.x * v;                                                \
+      S[4 * r4 + 1] = decay * S[4 * r4 + 1] + kk.y * v;                                        \
+      S[4 * r4 + 2] = decay * S[4 * r4 + 2] + kk.z * v;                                        \
+      S[4 * r4 + 3] = decay * S[4 * r4 + 3] + kk.w * v;                                        \
+      a0 += S[4 * r4] * qq.x;                                                                  \
+      a1 += S[4 * r4 + 1] * qq.y;                                                              \
+      a0 += S[4 * r4 + 2] * qq.z;                                                              \
+      a1 += S[4 * r4 + 3] * qq.w;                                                              \
+    }                                                                                          \
+    acc[c] = a0 + a1;                                                                          \
+  }
+      if (cn == RET_CHUNK) {
+#pragma unroll
+        for (int c = 0; c < RET_CHUNK; ++c) RET_TOKEN(c)
+      } else {
+#pragma unroll
+        for (int c = 0; c < RET_CHUNK; ++c) {
+          acc[c] = 0.f;
+          if (c < cn) RET_TOKEN(c)
+        }
+      }
+#undef RET_TOKEN
+      // the KS partial sums of a column, all tokens of the chunk at a time
+      for (int o = 1; o < KS; o <<= 1) {
+#pragma unroll
+        for (int c = 0; c < RET_CHUNK; ++c) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+      }
+      if (part == 0 && live) {
+#pragma unroll
+        for (int c = 0; c < RET_CHUNK; ++c)
+          if (c < cn) o_raw[(size_t)(t0 + s0 + c0 + c) * H * dv + (size_t)h * dv + col] = acc[c];
+      }
+    }
+    __syncthreads();                        // this buffer is filled again in the next round
   }
   if (live) {
 #pragma unroll
@@ -115,22 +201,42 @@ BF_EXPORT int bf_retention_scan(
     const void* proj, long long stride, long long q_off, long long k_off, long long v_off,
     const float* decays, const float* inv_freq, int rot_half, const int* positions, float* state,
     long long state_stride, const int* q_start, const int* state_slots, int n_slots, float* o_raw,
-    int B, int H, int dk, int dv, float k_scale, int act_dtype, int* err, cudaStream_t stream) {
-  if (B <= 0) return 0;
-  if (dk <= 0 || dv <= 0 || dk > 1024) return (int)cudaErrorInvalidValue;
+    float* qk, int T, int B, int H, int dk, int dv, float k_scale, int act_dtype, int* err,
+    cudaStream_t stream) {
+  // qk: scratch, float [T][2][H][dk]
+  if (B <= 0 || T <= 0) return 0;
+  if (dk <= 0 || dv <= 0 || dk > 1024 || !qk) return (int)cudaErrorInvalidValue;
+  {
+    const int threads = 128;
+    const long long blocks = ((long long)T * H * 32 + threads - 1) / threads;
+    if (act_dtype == BF_DTYPE_F32)
+      retention_encode_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+          (const float*)proj, stride, q_off, k_off, inv_freq, rot_half, positions, qk, T, H, dk,
+          k_scale);
+    else
+      retention_encode_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
+          (const __nv_bfloat16*)proj, stride, q_off, k_off, inv_freq, rot_half, positions, qk, T,
+          H, dk, k_scale);
+    const int e = bf_launch_status();
+    if (e) return e;
+  }
   const int R = dk <= 256 ? 8 : 32;
   int KS = 1;
   while (KS * R < dk) KS <<= 1;
   const int cols = RET_THREADS / KS;
   dim3 grid((dv + cols - 1) / cols, H, B);
-  const size_t smem = (size_t)(2 * RET_CHUNK * KS * R + RET_CHUNK * cols) * sizeof(float);
+  int stage = RET_STAGE;
+  while (stage > RET_CHUNK && (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float) > 72 * 1024)
+    stage >>= 1;
+  const size_t smem = (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
 #define RET_GO(AT, RR)                                                                        \
   if (smem > 48 * 1024)                                                                        \
     cudaFuncSetAttribute(retention_scan_kernel<AT, RR>,                                        \
                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
   retention_scan_kernel<AT, RR><<<grid, RET_THREADS, smem, stream>>>(                          \
-      (const AT*)proj, stride, q_off, k_off, v_off, decays, inv_freq, rot_half, positions,     \
-      state, state_stride, q_start, state_slots, n_slots, o_raw, H, dk, dv, KS, k_scale, err)
+      (const AT*)proj, stride, v_off, qk, decays, state, state_stride, q_start, state_slots,   \
+      n_slots, o_raw, H, dk, dv, KS, stage, err)
   if (act_dtype == BF_DTYPE_F32) {
     if (R == 8) { RET_GO(float, 8); } else { RET_GO(float, 32); }
   } else {
