@@ -12,22 +12,51 @@
 // them there.  bf_conv_state_shift, launched after the encode kernel, moves the step's last
 // rows into the state.
 //
-// One warp per (token, head); heads are counted q heads, then k heads, then v heads.  All
+// One warp per (token, head); heads are counted q heads, then k heads, then v heads.  The
+// cosines and sines of a token's angles are taken once for all its heads, by a small kernel
+// in front.  All
 // arithmetic is float; only the projection's values and the stored results have the
 // activation type.
 #include "common.cuh"
 
 #define CE_MAX_TAPS 8
 
+// cos and sin of position x frequency for every token of the step, once, for all heads:
+// table [T][rot_half] of (cos, sin).
+__global__ void rope_table_kernel(const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int T, int rot_half,
+                                  float2* __restrict__ table) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * rot_half) return;
+  const int t = i / rot_half, m = i - t * rot_half;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[m], &sn, &cs);
+  table[i] = make_float2(cs, sn);
+}
+
+// two neighbouring values of the activation type
+__device__ __forceinline__ float2 ce_ld2(const float* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+__device__ __forceinline__ float2 ce_ld2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void ce_st2(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+__device__ __forceinline__ void ce_st2(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 template <typename A>
 __global__ void conv_encode_kernel(
     const A* __restrict__ proj, long long stride, const float* __restrict__ conv_w, int taps,
     const float* __restrict__ state, long long state_stride, const int* __restrict__ state_slots,
     int n_state_slots, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-    const float* __restrict__ inv_freq, int rot_half, const int* __restrict__ positions,
-    const int* __restrict__ slots, A* __restrict__ q_out, long long q_stride,
-    A* __restrict__ k_cache, A* __restrict__ v_cache, int T, int nh, int nkv, int dk, int dv,
-    int page_size, long long num_slots, int unit_norm, float eps, int* __restrict__ err) {
+    const float2* __restrict__ rope, int rot_half, const int* __restrict__ slots,
+    A* __restrict__ q_out, long long q_stride, A* __restrict__ k_cache, A* __restrict__ v_cache,
+    int T, int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm,
+    float eps, int vec2, int* __restrict__ err) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = nh + 2 * nkv;
@@ -52,33 +81,53 @@ __global__ void conv_encode_kernel(
     if (slot < 0 || slot >= n_state_slots) { atomicOr(err, BF_ERR_SLOT); slot = 0; }
   }
   const float* st = state + (size_t)slot * state_stride;
-  for (int i = lane; i < d; i += 32) {
-    const int c = c0 + i;
-    float y;
-    if (taps > 1) {
-      y = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int src = local - (taps - 1) + j;       // index inside the portion
-        float u;
-        if (src >= 0) u = bf_ld(proj + (size_t)(t - (taps - 1) + j) * stride + c);
-        else u = st[(size_t)(taps - 1 + src) * C + c];
-        y += conv_w[(size_t)c * taps + j] * u;
+  if (vec2) {                                  // two neighbouring channels a lane and trip
+    for (int i = 2 * lane; i < d; i += 64) {
+      const int c = c0 + i;
+      float2 y;
+      if (taps > 1) {
+        y = make_float2(0.f, 0.f);
+        for (int j = 0; j < taps; ++j) {
+          const int src = local - (taps - 1) + j;     // index inside the portion
+          const float2 u = src >= 0 ? ce_ld2(proj + (size_t)(t - (taps - 1) + j) * stride + c)
+                                    : ce_ld2(st + (size_t)(taps - 1 + src) * C + c);
+          y.x += conv_w[(size_t)c * taps + j] * u.x;
+          y.y += conv_w[(size_t)(c + 1) * taps + j] * u.y;
+        }
+      } else {
+        y = ce_ld2(proj + (size_t)t * stride + c);
       }
-    } else {
-      y = bf_ld(proj + (size_t)t * stride + c);
+      buf[i] = y.x;
+      buf[i + 1] = y.y;
     }
-    buf[i] = y;
+  } else {
+    for (int i = lane; i < d; i += 32) {
+      const int c = c0 + i;
+      float y;
+      if (taps > 1) {
+        y = 0.f;
+        for (int j = 0; j < taps; ++j) {
+          const int src = local - (taps - 1) + j;     // index inside the portion
+          float u;
+          if (src >= 0) u = bf_ld(proj + (size_t)(t - (taps - 1) + j) * stride + c);
+          else u = st[(size_t)(taps - 1 + src) * C + c];
+          y += conv_w[(size_t)c * taps + j] * u;
+        }
+      } else {
+        y = bf_ld(proj + (size_t)t * stride + c);
+      }
+      buf[i] = y;
+    }
   }
   __syncwarp();
   float ss = 0.f;
-  const float pos = (float)positions[t];
   const bool turn = kind < 2 && rot_half > 0;
+  const float2* cs_sn = rope + (size_t)t * rot_half;
   for (int i = lane; i < d; i += 32) {
     float y = buf[i];
     if (turn && i < 2 * rot_half) {
       const int m = i < rot_half ? i : i - rot_half;
-      float sn, cs;
-      sincosf(pos * inv_freq[m], &sn, &cs);
+      const float cs = cs_sn[m].x, sn = cs_sn[m].y;
       const float other = i < rot_half ? buf[i + rot_half] : buf[i - rot_half];
       y = i < rot_half ? y * cs - other * sn : y * cs + other * sn;
     }
@@ -90,7 +139,10 @@ __global__ void conv_encode_kernel(
   if (kind < 2 && unit_norm) f = rsqrtf(warp_sum(ss) / (float)d + eps);
   if (kind == 0) {
     A* o = q_out + (size_t)t * q_stride + (size_t)head * dk;
-    for (int i = lane; i < d; i += 32) bf_st(o + i, res[i] * f);
+    if (vec2 && (q_stride & 1) == 0)
+      for (int i = 2 * lane; i < d; i += 64) ce_st2(o + i, res[i] * f, res[i + 1] * f);
+    else
+      for (int i = lane; i < d; i += 32) bf_st(o + i, res[i] * f);
     return;
   }
   if (!k_cache) return;
@@ -98,7 +150,10 @@ __global__ void conv_encode_kernel(
   if (s < 0 || s >= num_slots) { if (lane == 0) atomicOr(err, BF_ERR_SLOT); return; }
   const long long page = s / page_size, off = s % page_size;
   A* o = (kind == 1 ? k_cache : v_cache) + ((page * nkv + head) * page_size + off) * d;
-  for (int i = lane; i < d; i += 32) bf_st(o + i, res[i] * f);
+  if (vec2)
+    for (int i = 2 * lane; i < d; i += 64) ce_st2(o + i, res[i] * f, res[i + 1] * f);
+  else
+    for (int i = lane; i < d; i += 32) bf_st(o + i, res[i] * f);
 }
 
 BF_EXPORT int bf_conv_encode(
@@ -107,9 +162,24 @@ BF_EXPORT int bf_conv_encode(
     const int* q_start, const float* inv_freq, int rot_half, const int* positions,
     const int* slots, void* q_out, long long q_stride, void* k_cache, void* v_cache, int T,
     int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm, float eps,
-    int act_dtype, int* err, cudaStream_t stream) {
+    int act_dtype, float* rope_table, int* err, cudaStream_t stream) {
+  // rope_table: scratch, float [T][rot_half][2] (unused without a rotation)
   if (T <= 0) return 0;
   if (taps > CE_MAX_TAPS || (taps > 1 && (!conv_w || !state))) return (int)cudaErrorInvalidValue;
+  if (rot_half > 0) {
+    if (!rope_table) return (int)cudaErrorInvalidValue;
+    const int n = T * rot_half;
+    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, T, rot_half,
+                                                          (float2*)rope_table);
+    const int e = bf_launch_status();
+    if (e) return e;
+  }
+  // pairs of channels where every row and head starts at an even element and address
+  const int esz = act_dtype == BF_DTYPE_F32 ? 4 : 2;
+  const int vec2 = (dk % 2 == 0 && dv % 2 == 0 && stride % 2 == 0 && state_stride % 2 == 0 &&
+                    ((uintptr_t)proj % (2 * esz)) == 0 && ((uintptr_t)q_out % (2 * esz)) == 0 &&
+                    ((uintptr_t)k_cache % (2 * esz)) == 0 && ((uintptr_t)v_cache % (2 * esz)) == 0 &&
+                    ((uintptr_t)state % 8) == 0) ? 1 : 0;
   const int warps = 4;
   const long long items = (long long)T * (nh + 2 * nkv);
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
@@ -118,15 +188,15 @@ BF_EXPORT int bf_conv_encode(
   if (act_dtype == BF_DTYPE_F32)
     conv_encode_kernel<float><<<blocks, warps * 32, smem, stream>>>(
         (const float*)proj, stride, conv_w, taps, state, state_stride, state_slots, n_state_slots,
-        seq_of_token, q_start, inv_freq, rot_half, positions, slots, (float*)q_out, q_stride,
-        (float*)k_cache, (float*)v_cache, T, nh, nkv, dk, dv, page_size, num_slots, unit_norm,
-        eps, err);
+        seq_of_token, q_start, (const float2*)rope_table, rot_half, slots, (float*)q_out,
+        q_stride, (float*)k_cache, (float*)v_cache, T, nh, nkv, dk, dv, page_size, num_slots,
+        unit_norm, eps, vec2, err);
   else
     conv_encode_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, conv_w, taps, state, state_stride, state_slots,
-        n_state_slots, seq_of_token, q_start, inv_freq, rot_half, positions, slots,
+        n_state_slots, seq_of_token, q_start, (const float2*)rope_table, rot_half, slots,
         (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, nh,
-        nkv, dk, dv, page_size, num_slots, unit_norm, eps, err);
+        nkv, dk, dv, page_size, num_slots, unit_norm, eps, vec2, err);
   return bf_launch_status();
 }
 

@@ -465,14 +465,17 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
     num_slots = k_cache.shape[0] * page_size if k_cache is not None else 0
     if k_cache is not None and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise KernelError("cache pages must be contiguous")
+    # cosines and sines of every token's angles, written by a small kernel in front
+    table = (torch.empty((T, rot_half, 2), dtype=torch.float32, device=proj.device)
+             if rot_half else None)
     _run("conv_encode", lib().bf_conv_encode, _ptr(proj), _c_ll(proj.stride(0)), _ptr(conv_w),
          _c_int(taps), _ptr(state), _c_ll(state.stride(0) if state is not None else 0),
          _ptr(state_slots), _c_int(state.shape[0] if state is not None else 0),
          _ptr(seq_of_token), _ptr(q_start), _ptr(inv_freq), _c_int(rot_half), _ptr(positions),
          _ptr(slots), _ptr(q_out), _c_ll(q_out.stride(0)), _ptr(k_cache), _ptr(v_cache), _c_int(T),
          _c_int(nh), _c_int(nkv), _c_int(dk), _c_int(dv), _c_int(page_size), _c_ll(num_slots),
-         _c_int(1 if unit_norm else 0), _c_float(eps), _c_int(_dtype_code(proj)), _ptr(err),
-         _stream())
+         _c_int(1 if unit_norm else 0), _c_float(eps), _c_int(_dtype_code(proj)), _ptr(table),
+         _ptr(err), _stream())
 
 
 def conv_state_shift(proj: torch.Tensor, state: torch.Tensor, state_slots: torch.Tensor,
@@ -497,13 +500,14 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
                    inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
                    state: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor,
                    o_raw: torch.Tensor, B: int, heads: int, dk: int, dv: int, k_scale: float,
-                   err: torch.Tensor) -> None:
+                   err: torch.Tensor, max_q: int = 0) -> None:
     """The recurrence ``S <- decay_h S + k v^T, o = S^T q`` over every request's tokens of the
     step.  ``proj`` rows hold q (``heads dk`` numbers from column ``q_off``), k (from
     ``k_off``) and v (``heads dv`` from ``v_off``); q and k are turned by the position
     (``inv_freq`` float32, None: not) and k multiplied by ``k_scale``.  ``state`` float32
     ``[slots, heads * dv * dk]`` (a column block of the slots' storage); ``o_raw`` float32
-    ``[T, heads dv]``."""
+    ``[T, heads dv]``.  ``max_q``: the most tokens one request brings to the step, if the
+    caller knows it (0: not known)."""
     _want(decays, torch.float32, "decays"); _want(o_raw, torch.float32, "o_raw")
     if proj.stride(1) != 1 or dk > RETENTION_MAX_QK_DIM:
         raise KernelError(f"retention_scan: contiguous rows and a key size of at most "
@@ -521,8 +525,8 @@ def retention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay
     _run("retention_scan", lib().bf_retention_scan, _ptr(proj), _c_ll(proj.stride(0)),
          _c_ll(q_off), _c_ll(k_off), _c_ll(v_off), _ptr(decays), _ptr(inv_freq), _c_int(rot_half),
          _ptr(positions), _ptr(state), _c_ll(state.stride(0)), _ptr(q_start), _ptr(state_slots),
-         _c_int(state.shape[0]), _ptr(o_raw), _ptr(qk), _c_int(T), _c_int(B), _c_int(heads),
-         _c_int(dk), _c_int(dv), _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err),
+         _c_int(state.shape[0]), _ptr(o_raw), _ptr(qk), _c_int(T), _c_int(B),
+         _c_int(max_q if max_q > 0 else T), _c_int(heads), _c_int(dk), _c_int(dv), _c_float(k_scale), _c_int(_dtype_code(proj)), _ptr(err),
          _stream())
     global _launches
     _launches += 1          # two kernels: the rotation and the scan

@@ -95,11 +95,24 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
   const float decay = decays[h];
   float* sp = state + (size_t)slot * state_stride + (size_t)h * dv * dk + (size_t)part * R;
   float S[CV][R];
+  // whole rows of four floats where the sizes and the slot's address allow it
+  const bool st16 = dkp == dk && (dk & 3) == 0 && (state_stride & 3) == 0 &&
+                    (((uintptr_t)state) & 15) == 0;
 #pragma unroll
-  for (int j = 0; j < CV; ++j)
+  for (int j = 0; j < CV; ++j) {
+    if (st16 && col + j < dv) {
+      const float4* s4 = reinterpret_cast<const float4*>(sp + (size_t)(col + j) * dk);
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-      S[j][r] = (col + j < dv && part * R + r < dk) ? sp[(size_t)(col + j) * dk + r] : 0.f;
+      for (int r4 = 0; r4 < R / 4; ++r4) {
+        const float4 x = s4[r4];
+        S[j][4 * r4] = x.x; S[j][4 * r4 + 1] = x.y; S[j][4 * r4 + 2] = x.z; S[j][4 * r4 + 3] = x.w;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        S[j][r] = (col + j < dv && part * R + r < dk) ? sp[(size_t)(col + j) * dk + r] : 0.f;
+    }
+  }
 
   // A stage on its way into buffer `buf`: q and k rows by asynchronous 16-byte copies where
   // the rows allow it, v (which changes type) through registers.
@@ -207,19 +220,28 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     __syncthreads();                        // this buffer is filled again in the next round
   }
 #pragma unroll
-  for (int j = 0; j < CV; ++j)
+  for (int j = 0; j < CV; ++j) {
+    if (st16 && col + j < dv) {
+      float4* s4 = reinterpret_cast<float4*>(sp + (size_t)(col + j) * dk);
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (col + j < dv && part * R + r < dk) sp[(size_t)(col + j) * dk + r] = S[j][r];
+      for (int r4 = 0; r4 < R / 4; ++r4)
+        s4[r4] = make_float4(S[j][4 * r4], S[j][4 * r4 + 1], S[j][4 * r4 + 2], S[j][4 * r4 + 3]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (col + j < dv && part * R + r < dk) sp[(size_t)(col + j) * dk + r] = S[j][r];
+    }
+  }
 }
 
 BF_EXPORT int bf_retention_scan(
     const void* proj, long long stride, long long q_off, long long k_off, long long v_off,
     const float* decays, const float* inv_freq, int rot_half, const int* positions, float* state,
     long long state_stride, const int* q_start, const int* state_slots, int n_slots, float* o_raw,
-    float* qk, int T, int B, int H, int dk, int dv, float k_scale, int act_dtype, int* err,
-    cudaStream_t stream) {
-  // qk: scratch, float [T][2][H][dk]
+    float* qk, int T, int B, int max_q, int H, int dk, int dv, float k_scale, int act_dtype,
+    int* err, cudaStream_t stream) {
+  // qk: scratch, float [T][2][H][dk]; max_q: the most tokens one request brings (a hint that
+  // sizes the staging buffers: single tokens leave room for more blocks an SM)
   if (B <= 0 || T <= 0) return 0;
   if (dk <= 0 || dv <= 0 || dk > 1024 || !qk) return (int)cudaErrorInvalidValue;
   {
@@ -239,17 +261,15 @@ BF_EXPORT int bf_retention_scan(
   const int R = dk <= 256 ? 8 : 32;
   int KS = 1;
   while (KS * R < dk) KS <<= 1;
-  // A tile of four columns a lane (a quarter of the fetches of k and q per multiply-add, a
-  // quarter of the warps) once one column a lane gives more blocks than are resident at a
-  // time.  Measured, 2,048 tokens of heads of 128 x 256: 8 heads 0.52 ms with one column,
-  // 0.76 with four; 16 heads 1.3 against 0.92 (and four elements a lane instead of eight:
-  // 0.67 and 1.12).  Every column's sum has the same order either way.
-  const int cols1 = RET_THREADS / KS;
-  const bool many = (long long)B * H * ((dv + cols1 - 1) / cols1) > 3LL * 148;
-  const int CV = (R == 8 && dv % 4 == 0 && many) ? 4 : 1;
+  // A tile of two columns a lane: half the fetches of k and q per multiply-add, half the
+  // warps.  Measured, 2,048 tokens of heads of 128 x 256, one / two / four columns a lane:
+  // 8 heads 0.52 / 0.44 / 0.79 ms, 16 heads 1.35 / 0.67 / 0.95 ms; 8 single tokens 30 / 26 /
+  // 28 us and 45 / 34 / 35 us.  Every column's sum has the same order either way.
+  const int CV = (R == 8 && dv % 2 == 0) ? 2 : 1;
   const int cols = RET_THREADS / KS * CV;
   dim3 grid((dv + cols - 1) / cols, H, B);
   int stage = RET_STAGE;
+  while (stage > RET_CHUNK && stage / 2 >= max_q) stage >>= 1;
   while (stage > RET_CHUNK && (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float) > 72 * 1024)
     stage >>= 1;
   const size_t smem = (size_t)2 * stage * (2 * KS * R + cols) * sizeof(float);
@@ -265,7 +285,7 @@ BF_EXPORT int bf_retention_scan(
   }
 #define RET_PICK(AT)                                             \
   if (R == 32) RET_GO(AT, 32, 1)                                  \
-  else if (CV == 4) RET_GO(AT, 8, 4)                              \
+  else if (CV == 2) RET_GO(AT, 8, 2)                              \
   else RET_GO(AT, 8, 1)
   if (act_dtype == BF_DTYPE_F32) {
     RET_PICK(float)

@@ -78,7 +78,8 @@ class RetentionMixer(Mixer):
         inv = self.position.inv_freq if self.position is not None else None
         ops.retention_scan(proj, 0, self.qk_size, 2 * self.qk_size, self.decays, inv,
                            ctx.positions, view.state, ctx.q_start, ctx.state_slots, o_raw, ctx.B,
-                           self.heads, self.dk, self.dv, self.dk ** -0.5, ctx.err)
+                           self.heads, self.dk, self.dv, self.dk ** -0.5, ctx.err,
+                           max_q=1 if ctx.decode_only else ctx.max_q_len)
         ops.retention_out(o_raw, proj, 2 * self.qk_size + self.v_size, out, self.heads, self.dv,
                           self.spec.norm_eps, out_scale)
 
