@@ -1,8 +1,8 @@
 // What lies between the q/k/v projection and the attention of a mixer whose projections pass
 // a short causal convolution over time: convolution per channel, rotation of q and k, a
 // weightless RMS norm of each q and k head after the rotation, q to its buffer, k and v into
-// the cache pages.  Every step is optional (taps 0: no convolution; rot_half 0: no rotation;
-// unit_norm 0: no norm).
+// the cache pages.  Every step is optional (taps 0: no convolution, 1: a factor per channel
+// and no state; rot_half 0: no rotation; unit_norm 0: no norm).
 //
 //   y_t[c] = sum_j w[c, j] * u_{t - taps + 1 + j}[c],   j = 0 .. taps-1
 //
@@ -19,7 +19,7 @@
 // activation type.
 #include "common.cuh"
 
-#define CE_MAX_TAPS 8
+#define CE_MAX_TAPS 16
 
 // cos and sin of position x frequency for every token of the step, once, for all heads:
 // table [T][rot_half] of (cos, sin).
@@ -56,18 +56,16 @@ __global__ void conv_encode_kernel(
     const float2* __restrict__ rope, int rot_half, const int* __restrict__ slots,
     A* __restrict__ q_out, long long q_stride, A* __restrict__ k_cache, A* __restrict__ v_cache,
     int T, int nh, int nkv, int dk, int dv, int page_size, long long num_slots, int unit_norm,
-    float eps, int vec2, int* __restrict__ err) {
+    float eps, int vec2, int hpw, int* __restrict__ err) {
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = nh + 2 * nkv;
+  // a warp takes `hpw` heads of one token in turn: one round of lookups for all of them
+  const int groups = (heads_total + hpw - 1) / hpw;
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-  if (item >= (long long)T * heads_total) return;
-  const int t = (int)(item / heads_total), hs = (int)(item % heads_total);
+  if (item >= (long long)T * groups) return;
+  const int t = (int)(item / groups), hs0 = (int)(item % groups) * hpw;
   const int C = nh * dk + nkv * dk + nkv * dv;
-  int kind, head, d, c0;                       // 0 q, 1 k, 2 v; first channel of the head
-  if (hs < nh) { kind = 0; head = hs; d = dk; c0 = head * dk; }
-  else if (hs < nh + nkv) { kind = 1; head = hs - nh; d = dk; c0 = nh * dk + head * dk; }
-  else { kind = 2; head = hs - nh - nkv; d = dv; c0 = (nh + nkv) * dk + head * dv; }
   // per warp: the head after the convolution, and after the rotation
   const int dm = max(dk, dv);
   float* buf = sh + (size_t)warp * 2 * dm;
@@ -81,11 +79,18 @@ __global__ void conv_encode_kernel(
     if (slot < 0 || slot >= n_state_slots) { atomicOr(err, BF_ERR_SLOT); slot = 0; }
   }
   const float* st = state + (size_t)slot * state_stride;
+  const long long cache_slot = k_cache ? slots[t] : 0;
+  for (int hs = hs0; hs < min(hs0 + hpw, heads_total); ++hs) {
+  __syncwarp();                                // the last head's readers of buf and res are done
+  int kind, head, d, c0;                       // 0 q, 1 k, 2 v; first channel of the head
+  if (hs < nh) { kind = 0; head = hs; d = dk; c0 = head * dk; }
+  else if (hs < nh + nkv) { kind = 1; head = hs - nh; d = dk; c0 = nh * dk + head * dk; }
+  else { kind = 2; head = hs - nh - nkv; d = dv; c0 = (nh + nkv) * dk + head * dv; }
   if (vec2) {                                  // two neighbouring channels a lane and trip
     for (int i = 2 * lane; i < d; i += 64) {
       const int c = c0 + i;
       float2 y;
-      if (taps > 1) {
+      if (conv_w) {
         y = make_float2(0.f, 0.f);
         for (int j = 0; j < taps; ++j) {
           const int src = local - (taps - 1) + j;     // index inside the portion
@@ -104,7 +109,7 @@ __global__ void conv_encode_kernel(
     for (int i = lane; i < d; i += 32) {
       const int c = c0 + i;
       float y;
-      if (taps > 1) {
+      if (conv_w) {
         y = 0.f;
         for (int j = 0; j < taps; ++j) {
           const int src = local - (taps - 1) + j;     // index inside the portion
@@ -143,17 +148,18 @@ __global__ void conv_encode_kernel(
       for (int i = 2 * lane; i < d; i += 64) ce_st2(o + i, res[i] * f, res[i + 1] * f);
     else
       for (int i = lane; i < d; i += 32) bf_st(o + i, res[i] * f);
-    return;
+    continue;
   }
-  if (!k_cache) return;
-  const long long s = slots[t];
-  if (s < 0 || s >= num_slots) { if (lane == 0) atomicOr(err, BF_ERR_SLOT); return; }
+  if (!k_cache) continue;
+  const long long s = cache_slot;
+  if (s < 0 || s >= num_slots) { if (lane == 0) atomicOr(err, BF_ERR_SLOT); continue; }
   const long long page = s / page_size, off = s % page_size;
   A* o = (kind == 1 ? k_cache : v_cache) + ((page * nkv + head) * page_size + off) * d;
   if (vec2)
     for (int i = 2 * lane; i < d; i += 64) ce_st2(o + i, res[i] * f, res[i + 1] * f);
   else
     for (int i = lane; i < d; i += 32) bf_st(o + i, res[i] * f);
+  }
 }
 
 BF_EXPORT int bf_conv_encode(
@@ -165,7 +171,8 @@ BF_EXPORT int bf_conv_encode(
     int act_dtype, float* rope_table, int* err, cudaStream_t stream) {
   // rope_table: scratch, float [T][rot_half][2] (unused without a rotation)
   if (T <= 0) return 0;
-  if (taps > CE_MAX_TAPS || (taps > 1 && (!conv_w || !state))) return (int)cudaErrorInvalidValue;
+  if (taps > CE_MAX_TAPS || (taps > 1 && !state)) return (int)cudaErrorInvalidValue;
+  if (taps < 1) conv_w = nullptr;              // (one tap: a factor per channel, no state)
   if (rot_half > 0) {
     if (!rope_table) return (int)cudaErrorInvalidValue;
     const int n = T * rot_half;
@@ -181,7 +188,9 @@ BF_EXPORT int bf_conv_encode(
                     ((uintptr_t)k_cache % (2 * esz)) == 0 && ((uintptr_t)v_cache % (2 * esz)) == 0 &&
                     ((uintptr_t)state % 8) == 0) ? 1 : 0;
   const int warps = 4;
-  const long long items = (long long)T * (nh + 2 * nkv);
+  // many tokens: a warp walks four heads of its token (one round of lookups), else one
+  const int hpw = (long long)T * (nh + 2 * nkv) >= 16 * 148 * 16 ? 4 : 1;
+  const long long items = (long long)T * ((nh + 2 * nkv + hpw - 1) / hpw);
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   const int dm = dk > dv ? dk : dv;
   const size_t smem = (size_t)2 * warps * dm * sizeof(float);
@@ -190,13 +199,13 @@ BF_EXPORT int bf_conv_encode(
         (const float*)proj, stride, conv_w, taps, state, state_stride, state_slots, n_state_slots,
         seq_of_token, q_start, (const float2*)rope_table, rot_half, slots, (float*)q_out,
         q_stride, (float*)k_cache, (float*)v_cache, T, nh, nkv, dk, dv, page_size, num_slots,
-        unit_norm, eps, vec2, err);
+        unit_norm, eps, vec2, hpw, err);
   else
     conv_encode_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, conv_w, taps, state, state_stride, state_slots,
         n_state_slots, seq_of_token, q_start, (const float2*)rope_table, rot_half, slots,
         (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, nh,
-        nkv, dk, dv, page_size, num_slots, unit_norm, eps, vec2, err);
+        nkv, dk, dv, page_size, num_slots, unit_norm, eps, vec2, hpw, err);
   return bf_launch_status();
 }
 

@@ -1,6 +1,6 @@
 // Mixture of experts: the router and the weighting of the experts' activations.
 //
-// moe_route, one block per token: logits z = W_router h in float (h in the activation type,
+// moe_route, a block per token (or four): logits z = W_router h in float (h in the activation type,
 // the router's rows in float), the `top` largest chosen (the lower index wins a tie), their
 // weights the softmax over the chosen logits alone.  It leaves a dense row of weights
 // `route_w [T, E (+1)]` (zero for an expert not chosen) beside the chosen ids and weights;
@@ -16,44 +16,94 @@
 
 #include "common.cuh"
 
-// One block per token: the token's row goes to shared memory as float, the warps share the
-// router's rows out among them, and the first warp then chooses.
+// One block per MR_TOKENS tokens: their rows go to shared memory as float; every warp takes a
+// slice of the width and, row by row of the router, its share of each token's dot product
+// (a router row is fetched once for all the block's tokens); the shares are then added in
+// the warps' order, and one warp per token chooses.  A token's sums do not depend on which
+// other tokens share its block.
+#define MR_TOKENS 4
+#define MR_WARPS 8
+
 template <typename A>
-__global__ void moe_route_kernel(const A* __restrict__ h, long long stride,
-                                 const float* __restrict__ w, int T, int width, int E, int top,
-                                 int shared_gate, float* __restrict__ route_w,
-                                 int* __restrict__ top_ids, float* __restrict__ top_w) {
+__global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(
+    const A* __restrict__ h, long long stride, const float* __restrict__ w, int T, int width,
+    int E, int top, int shared_gate, int tokens_per_block, float* __restrict__ route_w,
+    int* __restrict__ top_ids, float* __restrict__ top_w) {
   extern __shared__ __align__(16) float sh[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * tokens_per_block;
+  const int nt = min(tokens_per_block, T - t0);
   const int rows = E + (shared_gate ? 1 : 0);
-  float* x = sh;                           // [width]
-  float* z = sh + ((width + 3) & ~3);      // [rows]
-  const A* src = h + (size_t)t * stride;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) x[c] = bf_ld(src + c);
-  __syncthreads();
-  const bool vec = (width & 3) == 0 && (((uintptr_t)w) & 15) == 0;
-  for (int e = warp; e < rows; e += warps) {
-    const float* wr = w + (size_t)e * width;
-    float a = 0.f;
-    if (vec) {
-      const float4* w4 = reinterpret_cast<const float4*>(wr);
-      const float4* x4 = reinterpret_cast<const float4*>(x);
-      for (int c = lane; c < (width >> 2); c += 32) {
-        const float4 p = w4[c], q = x4[c];
-        a += p.x * q.x;
-        a += p.y * q.y;
-        a += p.z * q.z;
-        a += p.w * q.w;
-      }
-    } else {
-      for (int c = lane; c < width; c += 32) a += wr[c] * x[c];
-    }
-    a = warp_sum(a);
-    if (lane == 0) z[e] = a;
+  const int wp = (width + 3) & ~3;
+  float* x = sh;                                   // [MR_TOKENS][wp]
+  float* part = sh + (size_t)MR_TOKENS * wp;       // [MR_WARPS][MR_TOKENS][rows]
+  float* zs = part + (size_t)MR_WARPS * MR_TOKENS * rows;   // [MR_TOKENS][rows]
+  for (int k = 0; k < nt; ++k) {
+    const A* src = h + (size_t)(t0 + k) * stride;
+#pragma unroll 8
+    for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)k * wp + c] = bf_ld(src + c);
   }
   __syncthreads();
-  if (warp != 0) return;
+  const bool vec = (width & 3) == 0 && (((uintptr_t)w) & 15) == 0;
+  // this warp's slice of the width, in units of four columns (or of one without `vec`)
+  const int units = vec ? width >> 2 : width;
+  const int per = (units + MR_WARPS - 1) / MR_WARPS;
+  const int lo = warp * per, hi = min(units, lo + per);
+  for (int e = 0; e < rows; ++e) {
+    const float* wr = w + (size_t)e * width;
+    float a[MR_TOKENS];
+#pragma unroll
+    for (int k = 0; k < MR_TOKENS; ++k) a[k] = 0.f;
+    if (vec) {
+      // four pieces of the row a lane at a time, all fetched before any is used: the round
+      // trips to L2 overlap (the sums keep the order of a plain walk)
+      const float4* w4 = reinterpret_cast<const float4*>(wr);
+      for (int c = lo + lane; c < hi; c += 128) {
+        float4 p[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          p[u] = c + 32 * u < hi ? w4[c + 32 * u] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c + 32 * u < hi) {
+#pragma unroll
+            for (int k = 0; k < MR_TOKENS; ++k) {
+              if (k < nt) {
+                const float4 q = reinterpret_cast<const float4*>(x + (size_t)k * wp)[c + 32 * u];
+                a[k] += p[u].x * q.x;
+                a[k] += p[u].y * q.y;
+                a[k] += p[u].z * q.z;
+                a[k] += p[u].w * q.w;
+              }
+            }
+          }
+        }
+      }
+    } else {
+      for (int c = lo + lane; c < hi; c += 32) {
+        const float p = wr[c];
+#pragma unroll
+        for (int k = 0; k < MR_TOKENS; ++k)
+          if (k < nt) a[k] += p * x[(size_t)k * wp + c];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < MR_TOKENS; ++k) {
+      const float r = warp_sum(a[k]);
+      if (lane == 0) part[((size_t)warp * MR_TOKENS + k) * rows + e] = r;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nt * rows; i += blockDim.x) {
+    const int k = i / rows, e = i - k * rows;
+    float r = 0.f;
+    for (int wv = 0; wv < MR_WARPS; ++wv) r += part[((size_t)wv * MR_TOKENS + k) * rows + e];
+    zs[(size_t)k * rows + e] = r;
+  }
+  __syncthreads();
+  if (warp >= nt) return;
+  const int t = t0 + warp;
+  float* z = zs + (size_t)warp * rows;
   float* rw = route_w + (size_t)t * rows;
   for (int e = lane; e < rows; e += 32) rw[e] = 0.f;
   if (shared_gate && lane == 0) rw[E] = 1.f / (1.f + expf(-z[E]));
@@ -97,16 +147,25 @@ BF_EXPORT int bf_moe_route(const void* h, long long stride, const float* w, int 
   if (T <= 0) return 0;
   if (top < 1 || top > E) return (int)cudaErrorInvalidValue;
   const int rows = E + (shared_gate ? 1 : 0);
-  const int warps = rows >= 8 ? 8 : 4;
-  const size_t smem = (size_t)(((width + 3) & ~3) + rows) * sizeof(float);
-  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-  if (act_dtype == BF_DTYPE_F32)
-    moe_route_kernel<float><<<T, warps * 32, smem, stream>>>(
-        (const float*)h, stride, w, T, width, E, top, shared_gate, route_w, top_ids, top_w);
-  else
-    moe_route_kernel<__nv_bfloat16><<<T, warps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)h, stride, w, T, width, E, top, shared_gate, route_w, top_ids,
-        top_w);
+  // few tokens: one a block, so that the step's blocks are many; else a router row serves four
+  const int tpb = T >= 4 * 148 ? MR_TOKENS : 1;
+  const size_t smem = ((size_t)MR_TOKENS * ((width + 3) & ~3) +
+                       (size_t)(MR_WARPS + 1) * MR_TOKENS * rows) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const unsigned blocks = (unsigned)((T + tpb - 1) / tpb);
+  if (act_dtype == BF_DTYPE_F32) {
+    auto k = moe_route_kernel<float>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<blocks, MR_WARPS * 32, smem, stream>>>((const float*)h, stride, w, T, width, E, top,
+                                               shared_gate, tpb, route_w, top_ids, top_w);
+  } else {
+    auto k = moe_route_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<blocks, MR_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)h, stride, w, T, width, E,
+                                               top, shared_gate, tpb, route_w, top_ids, top_w);
+  }
   return bf_launch_status();
 }
 

@@ -426,7 +426,7 @@ def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor],
 
 
 # --------------------------------- projections that pass a short convolution over time
-CONV_MAX_TAPS = 8
+CONV_MAX_TAPS = 16
 
 
 def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
@@ -439,7 +439,7 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
                 err: torch.Tensor) -> None:
     """``proj`` rows hold ``[q: nh dk | k: nkv dk | v: nkv dv]`` (a column block of a wider
     buffer is fine).  Per channel a causal convolution over the request's tokens with
-    ``conv_w`` float32 ``[channels, taps]`` (``taps`` <= 1: none), whose reach behind the
+    ``conv_w`` float32 ``[channels, taps]`` (``taps`` 0: none), whose reach behind the
     step's first row is read from ``state`` float32 ``[slots, (taps-1) * channels]`` (a column
     block of the slots' storage); then q and k turned by the position (``inv_freq``), each
     head of them divided by its root mean square when ``unit_norm``; q to ``q_out``, k and v
@@ -450,10 +450,11 @@ def conv_encode(proj: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int,
         raise KernelError("conv_encode: proj must be [T, nh dk + nkv (dk + dv)] with contiguous rows")
     if taps > CONV_MAX_TAPS:
         raise KernelError(f"conv_encode: at most {CONV_MAX_TAPS} taps")
-    if taps > 1:
+    if taps >= 1:
         _want(conv_w, torch.float32, "conv_w")
         if tuple(conv_w.shape) != (C, taps):
             raise KernelError("conv_encode: conv_w must be [channels, taps]")
+    if taps > 1:
         if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] != (taps - 1) * C:
             raise KernelError("conv_encode: state must be float32 [slots, (taps-1) * channels]")
     if inv_freq is not None:

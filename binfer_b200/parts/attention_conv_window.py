@@ -49,7 +49,7 @@ class ConvWindowAttention(Mixer):
                                             spec.value_dim)
         self.q_size, self.k_size, self.v_size = self.H * self.dk, self.G * self.dk, self.G * self.dv
         self.channels = self.q_size + self.k_size + self.v_size
-        self.taps = spec.conv_taps if spec.conv_taps > 1 else 0
+        self.taps = max(0, int(spec.conv_taps))     # one tap: a factor per channel, no state
         self.position = (build_position(spec.position, self.dk, env)
                          if spec.position is not None else None)
         if self.position is not None and self.position.inv_freq is None:
@@ -98,7 +98,7 @@ class ConvWindowAttention(Mixer):
                       keep_first=s.keep_first if s.window is not None else 0)
 
     def state_need(self) -> Optional[StateNeed]:
-        if not self.taps:
+        if self.taps <= 1:
             return None
         return StateNeed(((self.taps - 1) * self.channels,), "float32")
 
@@ -117,12 +117,12 @@ class ConvWindowAttention(Mixer):
             raise ValueError("this attention keeps a cache of its own")
         q = torch.empty((T, self.q_size), dtype=proj.dtype, device=proj.device)
         inv = self.position.inv_freq if self.position is not None else None
-        state = view.state if self.taps else None
+        state = view.state if self.taps > 1 else None
         ops.conv_encode(proj, self.conv_w, self.taps, state, ctx.state_slots, ctx.seq_of_token,
                         ctx.q_start, inv, ctx.positions, ctx.slots[g], q, view.k_cache,
                         view.v_cache, self.H, self.G, self.dk, self.dv, s.unit_norm, s.norm_eps,
                         ctx.err)
-        if self.taps:
+        if self.taps > 1:
             ops.conv_state_shift(proj, state, ctx.state_slots, ctx.q_start, ctx.B, self.taps)
         keep = s.keep_first if s.window is not None else 0
         if (TENSOR_CORES and s.softmax_scale > 0

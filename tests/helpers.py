@@ -432,13 +432,13 @@ FIK_B = {"architecture": "Fikotar", "vocab": 211, "width": 48, "norm": {"eps": 1
                                _fik_right(2, 12, 20, (0.93, 0.9995), 4, base=500.0),
                                _fik_moe(6, 2, 32, 72), ls=0.5, rs=0.5)]}
 # sizes that are multiples of two only: a width of 50, heads of 10 and 6, a vocabulary of 131;
-# a window of one token
+# a window of one token; a convolution of one tap (a factor per channel)
 FIK_C = {"architecture": "Fikotar", "vocab": 131, "width": 50, "norm": {"eps": 1e-5},
          "logit_scale": 2.0,
          "layers": [_fik_layer(_fik_left(2, 1, 10, 6, 1, 2, 6, conv=2, base=3000.0),
                                _fik_right(2, 6, 10, (0.9, 0.8), 6, base=3000.0),
                                _fik_moe(2, 1, 34, 46), ls=1.0, rs=1.0),
-                    _fik_layer(_fik_left(5, 5, 10, 10, 13, 0, 10, conv=3, base=3000.0),
+                    _fik_layer(_fik_left(5, 5, 10, 10, 13, 0, 10, conv=1, base=3000.0),
                                _fik_right(1, 10, 6, (0.99,), 2, base=3000.0), None)]}
 # wider, for bfloat16: heads of 64 and 128, a window of 64 that keeps four tokens
 FIK_D = {"architecture": "Fikotar", "vocab": 500, "width": 256, "norm": {"eps": 1e-5},

@@ -88,7 +88,7 @@ def conv_window_attention(h, w: Dict[str, torch.Tensor], p: str, mx: dict, eps: 
     H, G = mx["heads"], mx.get("kv_heads") or mx["heads"]
     d, dv = mx["dim"], mx.get("vdim") or mx["dim"]
     q, k, v = h @ w[p + "q"].T, h @ w[p + "k"].T, h @ w[p + "v"].T
-    if int(mx.get("conv") or 0) > 1:
+    if int(mx.get("conv") or 0) >= 1:
         q, k, v = (causal_conv(q, w[p + "q.conv"]), causal_conv(k, w[p + "k.conv"]),
                    causal_conv(v, w[p + "v.conv"]))
     q = unit_rms(rotate(q.view(T, H, d), mx.get("rot")), eps)
