@@ -123,20 +123,26 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     float* qd = sh + (size_t)buf * buf_elems;
     float* kd = qd + stage * dkp;
     float* vd = kd + stage * dkp;
+    // In shared memory a token's k (and q) lies piece by piece of four floats in the order
+    // [r4][part]: the lanes of a column, which fetch piece r4 of their R elements together,
+    // then read neighbouring addresses (no bank conflicts), not addresses R floats apart.
     if (rows16) {
       const int d4 = dk >> 2;
       for (int idx = tid; idx < sn * d4; idx += RET_THREADS) {
         const int c = idx / d4, i = idx - c * d4;
+        const int at = c * d4 + (i % (R / 4)) * KS + i / (R / 4);
         const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * H + h) * dk + 4 * i;
-        ret_cp16(qd + 4 * idx, row);
-        ret_cp16(kd + 4 * idx, row + (size_t)H * dk);
+        ret_cp16(qd + 4 * at, row);
+        ret_cp16(kd + 4 * at, row + (size_t)H * dk);
       }
     } else {
       for (int idx = tid; idx < sn * dkp; idx += RET_THREADS) {
         const int c = idx / dkp, i = idx % dkp;
+        const int pt = i / R, r = i % R;
+        const int at = c * dkp + ((r >> 2) * KS + pt) * 4 + (r & 3);
         const float* row = qk + ((size_t)(t0 + s0 + c) * 2 * H + h) * dk;
-        qd[idx] = i < dk ? row[i] : 0.f;
-        kd[idx] = i < dk ? row[(size_t)H * dk + i] : 0.f;
+        qd[at] = i < dk ? row[i] : 0.f;
+        kd[at] = i < dk ? row[(size_t)H * dk + i] : 0.f;
       }
     }
     for (int idx = tid; idx < sn * cols; idx += RET_THREADS) {
@@ -165,41 +171,58 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
       const int cn = min(RET_CHUNK, sn - c0);
       float acc[RET_CHUNK][CV];
       // one token: the state's multiply-add and this lane's share of the token's dot products
-#define RET_TOKEN(c)                                                                          \
+      // A token's k, q and v are fetched one token ahead of their use (two sets of
+      // registers in turn), so that the shared-memory round trip runs under the token
+      // before; the state's own chain is one multiply-add a token (k v is formed beside it).
+      float4 kk[2][R / 4], qq[2][R / 4];
+      float vv[2][CV];
+#define RET_FETCH(c, bi)                                                                        \
   {                                                                                            \
-    float v[CV], a0[CV], a1[CV];                                                               \
-    _Pragma("unroll") for (int j = 0; j < CV; ++j) {                                           \
-      v[j] = vs[(c0 + c) * cols + cg * CV + j];                                                \
-      a0[j] = a1[j] = 0.f;                                                                     \
-    }                                                                                          \
-    const float4* qr = reinterpret_cast<const float4*>(qs + (c0 + c) * dkp + part * R);        \
-    const float4* kr = reinterpret_cast<const float4*>(ks_ + (c0 + c) * dkp + part * R);       \
+    const float4* qr = reinterpret_cast<const float4*>(qs + (c0 + (c)) * dkp) + part;          \
+    const float4* kr = reinterpret_cast<const float4*>(ks_ + (c0 + (c)) * dkp) + part;         \
     _Pragma("unroll") for (int r4 = 0; r4 < R / 4; ++r4) {                                     \
-      const float4 kk = kr[r4], qq = qr[r4];                                                   \
+      kk[bi][r4] = kr[r4 * KS];                                                                 \
+      qq[bi][r4] = qr[r4 * KS];                                                                 \
+    }                                                                                          \
+    _Pragma("unroll") for (int j = 0; j < CV; ++j) vv[bi][j] = vs[(c0 + (c)) * cols + cg * CV + j]; \
+  }
+#define RET_TOKEN(c, bi)                                                                        \
+  {                                                                                            \
+    float a0[CV], a1[CV];                                                                      \
+    _Pragma("unroll") for (int j = 0; j < CV; ++j) a0[j] = a1[j] = 0.f;                        \
+    _Pragma("unroll") for (int r4 = 0; r4 < R / 4; ++r4) {                                     \
       _Pragma("unroll") for (int j = 0; j < CV; ++j) {                                         \
-        S[j][4 * r4] = decay * S[j][4 * r4] + kk.x * v[j];                                     \
-        S[j][4 * r4 + 1] = decay * S[j][4 * r4 + 1] + kk.y * v[j];                             \
-        S[j][4 * r4 + 2] = decay * S[j][4 * r4 + 2] + kk.z * v[j];                             \
-        S[j][4 * r4 + 3] = decay * S[j][4 * r4 + 3] + kk.w * v[j];                             \
-        a0[j] += S[j][4 * r4] * qq.x;                                                          \
-        a1[j] += S[j][4 * r4 + 1] * qq.y;                                                      \
-        a0[j] += S[j][4 * r4 + 2] * qq.z;                                                      \
-        a1[j] += S[j][4 * r4 + 3] * qq.w;                                                      \
+        S[j][4 * r4] = fmaf(decay, S[j][4 * r4], kk[bi][r4].x * vv[bi][j]);                      \
+        S[j][4 * r4 + 1] = fmaf(decay, S[j][4 * r4 + 1], kk[bi][r4].y * vv[bi][j]);              \
+        S[j][4 * r4 + 2] = fmaf(decay, S[j][4 * r4 + 2], kk[bi][r4].z * vv[bi][j]);              \
+        S[j][4 * r4 + 3] = fmaf(decay, S[j][4 * r4 + 3], kk[bi][r4].w * vv[bi][j]);              \
+        a0[j] += S[j][4 * r4] * qq[bi][r4].x;                                                   \
+        a1[j] += S[j][4 * r4 + 1] * qq[bi][r4].y;                                               \
+        a0[j] += S[j][4 * r4 + 2] * qq[bi][r4].z;                                               \
+        a1[j] += S[j][4 * r4 + 3] * qq[bi][r4].w;                                               \
       }                                                                                        \
     }                                                                                          \
     _Pragma("unroll") for (int j = 0; j < CV; ++j) acc[c][j] = a0[j] + a1[j];                  \
   }
+      RET_FETCH(0, 0)
       if (cn == RET_CHUNK) {
 #pragma unroll
-        for (int c = 0; c < RET_CHUNK; ++c) RET_TOKEN(c)
+        for (int c = 0; c < RET_CHUNK; ++c) {
+          if (c + 1 < RET_CHUNK) RET_FETCH(c + 1, (c + 1) & 1)
+          RET_TOKEN(c, c & 1)
+        }
       } else {
 #pragma unroll
         for (int c = 0; c < RET_CHUNK; ++c) {
 #pragma unroll
           for (int j = 0; j < CV; ++j) acc[c][j] = 0.f;
-          if (c < cn) RET_TOKEN(c)
+          if (c < cn) {
+            if (c + 1 < cn) RET_FETCH(c + 1, (c + 1) & 1)
+            RET_TOKEN(c, c & 1)
+          }
         }
       }
+#undef RET_FETCH
 #undef RET_TOKEN
       // the KS partial sums of a column, all tokens of the chunk at a time
       for (int o = 1; o < KS; o <<= 1) {
