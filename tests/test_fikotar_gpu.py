@@ -239,12 +239,12 @@ def test_sink_and_first_tokens(cuda_device, tmp_path):
 @pytest.mark.parametrize("W,keep,T,marked", [
     (20, 5, 240, (4, 150)), (20, 5, 240, (5, 150)), (64, 70, 500, (69, 420)),
     (130, 3, 700, (500, 629)), (130, 3, 700, (499, 629)), (64, 0, 300, (100, 163)),
-    (1000, 2, 300, (0, 299))])
+    (1000, 2, 300, (0, 299)), (None, 0, 300, (10, 299))])
 def test_tensor_core_attention_beside_the_plain_kernel(cuda_device, tmp_path, W, keep, T, marked):
     """bfloat16: the tiled kernel and the one-warp-per-row kernel on the same one-layer model
     with a marked key at a window's or the kept tokens' edge, whole, cut and token by token
     (a single token's key tiles are shared out over CTAs and merged): both within rounding of
-    the plain implementation, and of each other."""
+    the plain implementation, and of each other.  (The last case has no window at all.)"""
     from binfer_b200.csrc import ops
     from binfer_b200.parts import attention_conv_window as mod
     from binfer_b200.profiling import Profiler
@@ -314,8 +314,9 @@ def plain_logits(tmp_path_factory):
 
 @pytest.mark.parametrize("which,dtype", [("A", torch.float32), ("B", torch.float32),
                                          ("C", torch.float32), ("A", torch.bfloat16),
-                                         ("B", torch.bfloat16), ("D", torch.bfloat16)],
-                         ids=["A-f32", "B-f32", "C-f32", "A-bf16", "B-bf16", "D-bf16"])
+                                         ("B", torch.bfloat16), ("C", torch.bfloat16),
+                                         ("D", torch.bfloat16)],
+                         ids=["A-f32", "B-f32", "C-f32", "A-bf16", "B-bf16", "C-bf16", "D-bf16"])
 @pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
 def test_replay(cuda_device, plain_logits, which, dtype, regime):
     """Seven requests through four state slots and page pools of exactly the peak need."""
