@@ -233,3 +233,187 @@ BF_EXPORT int bf_moe_act(const void* gu, const float* route_w, void* act, int T,
         (const __nv_bfloat16*)gu, route_w, (__nv_bfloat16*)act, T, F, E, ff, rw_cols);
   return bf_launch_status();
 }
+
+// ------------------------------------------------------------------ few tokens: chosen experts only
+// A step of very few tokens (a request decoding alone) should not read the experts that no
+// token chose.  moe_sparse_gate_up computes, per token and choice (the `top` chosen experts in
+// the router's order, then the shared expert if there is one), the expert's activations
+// times the token's weight for it, from the expert's rows of the stacked gate/up weight;
+// moe_sparse_down multiplies them with the expert's columns of the stacked down weight and
+// adds the choices up in that order.  One warp per output row, the token's input in shared
+// memory as float, 16-byte pieces of the rows where the sizes allow.
+//
+// act: [T][top * ff + ff_sh] (choice k at k * ff, the shared expert behind them).
+#define MS_WARPS 8
+#define MS_ROWS 4           // rows a warp takes in turn
+
+// Pieces of eight neighbouring values of a row as floats.
+__device__ __forceinline__ void ms_ld8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void ms_ld8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h2[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+
+// A row of n values of the activation type into shared memory as floats, by the whole block,
+// in pieces of eight where the row allows it.
+template <typename A>
+__device__ __forceinline__ void ms_stage(const A* __restrict__ src, float* __restrict__ dst,
+                                         int n) {
+  const int esz = (int)sizeof(A);
+  if ((n & 7) == 0 && (((uintptr_t)src) % (8 * esz)) == 0) {
+#pragma unroll 4
+    for (int c = threadIdx.x * 8; c < n; c += blockDim.x * 8) {
+      float v[8];
+      ms_ld8(src + c, v);
+      reinterpret_cast<float4*>(dst + c)[0] = make_float4(v[0], v[1], v[2], v[3]);
+      reinterpret_cast<float4*>(dst + c)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = bf_ld(src + c);
+  }
+}
+
+// NR rows at `w + r * row_stride` against the same x [n]: the rows' pieces of a trip are all
+// fetched before any is used, so that NR round trips to memory overlap.  Every row's sum has
+// the order of a plain strided walk followed by the warp's tree.
+template <typename A, int NR>
+__device__ __forceinline__ void ms_dots(const A* __restrict__ w, size_t row_stride, int rows,
+                                        const float* __restrict__ x, int n, int lane, bool vec,
+                                        float (&out)[NR]) {
+  float a[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) a[r] = 0.f;
+  if (vec) {
+    for (int c = lane * 8; c < n; c += 256) {
+      float p[NR][8];
+#pragma unroll
+      for (int r = 0; r < NR; ++r)
+        if (r < rows) ms_ld8(w + (size_t)r * row_stride + c, p[r]);
+      float q[8];
+      ms_ld8(x + c, q);
+#pragma unroll
+      for (int r = 0; r < NR; ++r)
+        if (r < rows) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[r] += p[r][j] * q[j];
+        }
+    }
+  } else {
+    for (int c = lane; c < n; c += 32)
+#pragma unroll
+      for (int r = 0; r < NR; ++r)
+        if (r < rows) a[r] += bf_ld(w + (size_t)r * row_stride + c) * x[c];
+  }
+#pragma unroll
+  for (int r = 0; r < NR; ++r) out[r] = warp_sum(a[r]);
+}
+
+// grid (row tiles, choices, T)
+template <typename A>
+__global__ void moe_sparse_gate_up_kernel(const A* __restrict__ h, long long stride,
+                                          const A* __restrict__ w_gu, int width, int F, int E,
+                                          int ff, int ff_sh, int top,
+                                          const int* __restrict__ top_ids,
+                                          const float* __restrict__ top_w,
+                                          const float* __restrict__ route_w, int rw_cols,
+                                          A* __restrict__ act) {
+  extern __shared__ __align__(16) float sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.z, k = blockIdx.y;
+  const bool shared = k == top;
+  const int n_rows = shared ? ff_sh : ff;
+  const int row0 = (blockIdx.x * MS_WARPS + warp) * MS_ROWS;
+  if (blockIdx.x * MS_WARPS * MS_ROWS >= n_rows) return;
+  ms_stage<A>(h + (size_t)t * stride, sh, width);
+  __syncthreads();
+  const int e = shared ? E : top_ids[(size_t)t * top + k];
+  const float wgt = shared ? (E < rw_cols ? route_w[(size_t)t * rw_cols + E] : 1.f)
+                           : top_w[(size_t)t * top + k];
+  const size_t base = shared ? (size_t)E * ff : (size_t)e * ff;      // the expert's first row
+  const bool vec = (width % 8) == 0 && (((uintptr_t)w_gu) & 15) == 0;
+  A* dst = act + (size_t)t * ((size_t)top * ff + ff_sh) + (shared ? (size_t)top * ff : (size_t)k * ff);
+  const int rows = min(MS_ROWS, n_rows - row0);
+  if (rows <= 0) return;
+  float g[MS_ROWS], u[MS_ROWS];
+  ms_dots<A, MS_ROWS>(w_gu + (base + row0) * width, (size_t)width, rows, sh, width, lane, vec, g);
+  ms_dots<A, MS_ROWS>(w_gu + ((size_t)F + base + row0) * width, (size_t)width, rows, sh, width,
+                      lane, vec, u);
+  if (lane == 0)
+    for (int r = 0; r < rows; ++r) bf_st(dst + row0 + r, g[r] / (1.f + expf(-g[r])) * u[r] * wgt);
+}
+
+// grid (row tiles, T)
+template <typename A>
+__global__ void moe_sparse_down_kernel(const A* __restrict__ act, const A* __restrict__ w_down,
+                                       int width, int F, int E, int ff, int ff_sh, int top,
+                                       const int* __restrict__ top_ids, A* __restrict__ out) {
+  extern __shared__ __align__(16) float sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.y;
+  const int n_act = top * ff + ff_sh;
+  ms_stage<A>(act + (size_t)t * n_act, sh, n_act);
+  __syncthreads();
+  const int row0 = (blockIdx.x * MS_WARPS + warp) * MS_ROWS;
+  const bool vec = (ff % 8) == 0 && (F % 8) == 0 && (((uintptr_t)w_down) & 15) == 0;
+  const int rows = min(MS_ROWS, width - row0);
+  if (rows <= 0) return;
+  const A* wr = w_down + (size_t)row0 * F;
+  float a[MS_ROWS], part[MS_ROWS];
+#pragma unroll
+  for (int r = 0; r < MS_ROWS; ++r) a[r] = 0.f;
+  for (int k = 0; k < top; ++k) {
+    ms_dots<A, MS_ROWS>(wr + (size_t)top_ids[(size_t)t * top + k] * ff, (size_t)F, rows,
+                        sh + (size_t)k * ff, ff, lane, vec, part);
+#pragma unroll
+    for (int r = 0; r < MS_ROWS; ++r) a[r] += part[r];
+  }
+  if (ff_sh) {
+    ms_dots<A, MS_ROWS>(wr + (size_t)E * ff, (size_t)F, rows, sh + (size_t)top * ff, ff_sh, lane,
+                        vec && (ff_sh % 8) == 0, part);
+#pragma unroll
+    for (int r = 0; r < MS_ROWS; ++r) a[r] += part[r];
+  }
+  if (lane == 0)
+    for (int r = 0; r < rows; ++r) bf_st(out + (size_t)t * width + row0 + r, a[r]);
+}
+
+BF_EXPORT int bf_moe_sparse(const void* h, long long stride, const void* w_gu, const void* w_down,
+                            const int* top_ids, const float* top_w, const float* route_w,
+                            int rw_cols, void* act, void* out, int T, int width, int E, int ff,
+                            int ff_sh, int top, int act_dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int F = E * ff + ff_sh;
+  const int choices = top + (ff_sh ? 1 : 0);
+  const int n_act = top * ff + ff_sh;
+  const int rows_max = ff > ff_sh ? ff : ff_sh;
+  const int per_block = MS_WARPS * MS_ROWS;
+  if ((size_t)width * 4 > 48 * 1024 || (size_t)n_act * 4 > 48 * 1024)
+    return (int)cudaErrorInvalidValue;
+  dim3 g1((rows_max + per_block - 1) / per_block, choices, T);
+  dim3 g2((width + per_block - 1) / per_block, T);
+  if (act_dtype == BF_DTYPE_F32) {
+    moe_sparse_gate_up_kernel<float><<<g1, MS_WARPS * 32, (size_t)width * 4, stream>>>(
+        (const float*)h, stride, (const float*)w_gu, width, F, E, ff, ff_sh, top, top_ids, top_w,
+        route_w, rw_cols, (float*)act);
+    moe_sparse_down_kernel<float><<<g2, MS_WARPS * 32, (size_t)n_act * 4, stream>>>(
+        (const float*)act, (const float*)w_down, width, F, E, ff, ff_sh, top, top_ids,
+        (float*)out);
+  } else {
+    moe_sparse_gate_up_kernel<__nv_bfloat16><<<g1, MS_WARPS * 32, (size_t)width * 4, stream>>>(
+        (const __nv_bfloat16*)h, stride, (const __nv_bfloat16*)w_gu, width, F, E, ff, ff_sh, top,
+        top_ids, top_w, route_w, rw_cols, (__nv_bfloat16*)act);
+    moe_sparse_down_kernel<__nv_bfloat16><<<g2, MS_WARPS * 32, (size_t)n_act * 4, stream>>>(
+        (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, width, F, E, ff, ff_sh, top,
+        top_ids, (__nv_bfloat16*)out);
+  }
+  return bf_launch_status();
+}

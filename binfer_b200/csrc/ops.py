@@ -580,6 +580,39 @@ def moe_act(gu: torch.Tensor, route_w: torch.Tensor, act: torch.Tensor, experts:
          _stream())
 
 
+def moe_sparse_takes(width: int, ff: int, ff_sh: int, top: int) -> bool:
+    """Whether :func:`moe_sparse` takes these sizes (a token's input and its chosen experts'
+    activations each fit a block's shared memory as float)."""
+    return width * 4 <= 48 * 1024 and (top * ff + ff_sh) * 4 <= 48 * 1024
+
+
+def moe_sparse(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+               top_ids: torch.Tensor, top_w: torch.Tensor, route_w: torch.Tensor,
+               out: torch.Tensor, experts: int, ff: int, ff_sh: int, top: int) -> None:
+    """The mixture's output for a step of very few tokens, reading only the experts that
+    were chosen (and the shared one): ``w_gate_up [2 F, width]`` and ``w_down [width, F]`` are
+    the stacked weights (``F = experts * ff + ff_sh``), ``top_ids``/``top_w``/``route_w`` what
+    :func:`moe_route` left; ``out [T, width]``."""
+    T, width = h.shape
+    F = experts * ff + ff_sh
+    if (tuple(w_gate_up.shape) != (2 * F, width) or tuple(w_down.shape) != (width, F)
+            or not w_gate_up.is_contiguous() or not w_down.is_contiguous()
+            or w_gate_up.dtype != h.dtype or w_down.dtype != h.dtype or h.stride(1) != 1
+            or not out.is_contiguous() or out.dtype != h.dtype):
+        raise KernelError("moe_sparse: stacked weights [2 F, width] and [width, F] of h's type")
+    if not moe_sparse_takes(width, ff, ff_sh, top):
+        raise KernelError("moe_sparse: sizes too large for a block's shared memory")
+    _want(top_ids, torch.int32, "top_ids"); _want(top_w, torch.float32, "top_w")
+    _want(route_w, torch.float32, "route_w")
+    act = torch.empty((T, top * ff + ff_sh), dtype=h.dtype, device=h.device)
+    _run("moe_sparse", lib().bf_moe_sparse, _ptr(h), _c_ll(h.stride(0)), _ptr(w_gate_up),
+         _ptr(w_down), _ptr(top_ids), _ptr(top_w), _ptr(route_w), _c_int(route_w.shape[1]),
+         _ptr(act), _ptr(out), _c_int(T), _c_int(width), _c_int(experts), _c_int(ff),
+         _c_int(ff_sh), _c_int(top), _c_int(_dtype_code(h)), _stream())
+    global _launches
+    _launches += 1          # two kernels
+
+
 # ----------------------------------------------------- norm on a sublayer's output
 def rmsnorm_add(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor,
                 reading: Optional[torch.Tensor], eps: float) -> None:

@@ -12,9 +12,14 @@ chosen); one product with the down projections laid side by side then sums the w
 experts in its own accumulation.  Unchosen experts cost arithmetic but no extra pass over
 memory, no token is moved, and a token's result does not depend on what else is in the
 batch.
+
+A step of very few tokens in bfloat16 (a request that decodes alone) would read every expert
+for nothing; there the chosen experts' rows alone are read, a warp per output row
+(``ops.moe_sparse``).  The float32 engine keeps the one path, so that its sums have one order.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List
 
 import torch
@@ -24,6 +29,10 @@ from ..csrc import ops
 from ..weights.loader import ParamSpec
 from .base import BuildEnv, FeedForward, StepContext, register_ffn
 from .linear import linear
+
+
+# BINFER_B200_MOE_SPARSE=0: every step computes every expert
+SPARSE = os.environ.get("BINFER_B200_MOE_SPARSE", "1") != "0"
 
 
 class MoEFeedForward(FeedForward):
@@ -80,6 +89,13 @@ class MoEFeedForward(FeedForward):
         top_w = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
         ops.moe_route(x, self.w_router, self.E, self.top, self.gated_shared, route_w, top_ids,
                       top_w)
+        if (SPARSE and x.dtype == torch.bfloat16 and 2 * T * self.top <= self.E
+                and ops.moe_sparse_takes(self.hidden, self.ff, self.ff_sh, self.top)):
+            # so few tokens that most experts are chosen by none: read the chosen ones alone
+            out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
+            ops.moe_sparse(x, self.w_gate_up, self.w_down, top_ids, top_w, route_w, out, self.E,
+                           self.ff, self.ff_sh, self.top)
+            return out
         gu = linear(x, self.w_gate_up)
         act = torch.empty((T, self.F), dtype=x.dtype, device=x.device)
         ops.moe_act(gu, route_w, act, self.E, self.ff)
